@@ -21,7 +21,7 @@ MODEL_REMAPPING = {
     "mistral": "llama",  # reference utils.py:15
 }
 
-SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2")
+SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn")
 
 
 @dataclass(frozen=True)
@@ -145,6 +145,10 @@ class ModelConfig:
     moe_layer_freq: int = 1
     first_k_dense_replace: int = 0
     norm_topk_prob: bool = False
+    # perelorn (hybrid stack: per-layer mixer / feed-forward specs, per-layer token input, logit scale)
+    layer_specs: Optional[list] = None
+    token_side_dim: int = 0
+    logit_scale: float = 1.0
     # quantisation (mlx affine) + sharding
     quantization: Optional[Dict[str, int]] = None
     start_layer: Optional[int] = None
@@ -155,6 +159,8 @@ class ModelConfig:
     @classmethod
     def from_dict(cls, d: Dict[str, Any]) -> "ModelConfig":
         d = dict(d)
+        if "model_type" not in d and str(d.get("architecture", "")).lower() == "perelorn":
+            d = _perelorn_flat(d)
         mt = d.get("model_type", "llama")
         if mt == "phi-msft":
             raise ValueError(
@@ -256,6 +262,39 @@ class ModelConfig:
             and i >= self.first_k_dense_replace
             and i % self.moe_layer_freq == 0
         )
+
+
+def _perelorn_flat(d: Dict[str, Any]) -> Dict[str, Any]:
+    """Perelorn's nested config.json (``layers`` = list of {type, mixer, mlp}; ``norm.eps``; ``token_side.dim``; ``vocab``;
+    ``width``; ``logit_scale``) -> the flat fields of :class:`ModelConfig`.  Every size is read from the file."""
+    layers = [dict(type=str(L["type"]), mixer=dict(L["mixer"]), mlp=(dict(L["mlp"]) if L.get("mlp") else None)) for L in d["layers"]]
+    for L in layers:
+        if L["type"] not in ("mamba2", "latent_attention", "lightning"):
+            raise ValueError(f"Perelorn: unknown mixer type '{L['type']}'")
+        if L["mlp"] is not None and L["mlp"].get("kind", "dense") != "dense":
+            raise ValueError(f"Perelorn: unknown feed-forward kind '{L['mlp'].get('kind')}'")
+    side = d.get("token_side") or {}
+    out = {k: v for k, v in d.items() if k not in ("architecture", "layers", "norm", "token_side", "vocab", "width", "logit_scale")}
+    ff = [L["mlp"]["ff"] for L in layers if L["mlp"]]
+    out.update(model_type="perelorn", hidden_size=int(d["width"]), vocab_size=int(d["vocab"]), num_hidden_layers=len(layers),
+               rms_norm_eps=float(d["norm"]["eps"]), layer_specs=layers, token_side_dim=int(side.get("dim", 0)),
+               logit_scale=float(d.get("logit_scale", 1.0)), intermediate_size=int(max(ff)) if ff else 0,
+               num_attention_heads=int(max(L["mixer"]["heads"] for L in layers)))
+    return out
+
+
+def perelorn_config(width=2048, vocab=32000, blocks=4, heads=16, ff=8192, side_dim=64, **overrides) -> Dict[str, Any]:
+    """A Perelorn config.json with layer sizes that resemble a real model: ``blocks`` x (mamba2, latent attention + feed-forward,
+    mamba2, lightning)."""
+    mamba = dict(type="mamba2", mixer=dict(conv=4, groups=1, heads=2 * width // 64, norm_groups=1, state=128, vdim=64), mlp=None)
+    attn = dict(type="latent_attention", mixer=dict(dim=128, heads=heads, kv_rank=512, q_rank=1536, rot=dict(base=10000.0, dims=64),
+                                                    rot_dim=64, scale=192 ** -0.5, vdim=128), mlp=dict(ff=ff, kind="dense"))
+    light = dict(type="lightning", mixer=dict(decay=[1.0 - 2.0 ** -(3 + 5 * h / max(1, heads - 1)) for h in range(heads)], dim=128,
+                                              heads=heads, vdim=128), mlp=None)
+    d = dict(architecture="Perelorn", layers=[mamba, attn, mamba, light] * blocks, logit_scale=1.0, norm=dict(eps=1e-5),
+             token_side=dict(dim=side_dim), vocab=vocab, width=width)
+    d.update(overrides)
+    return d
 
 
 def yarn_get_mscale(scale: float = 1.0, mscale: float = 1.0) -> float:

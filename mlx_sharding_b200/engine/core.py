@@ -22,7 +22,7 @@ from typing import Dict, List, Optional, Sequence
 import torch
 
 from ..ops.meta import BatchMeta
-from .kv_cache import PageAllocator, PrefixCache, SequenceTable
+from .kv_cache import PageAllocator, PrefixCache, SequenceTable, SlotAllocator
 from .sampler import SamplingParams
 
 
@@ -119,7 +119,7 @@ def stopping_criteria(tokens: List[int], stop_id_sequences: List[List[int]], eos
 class LLMEngine:
     def __init__(self, pipeline, num_pages: int, page_size: int = 64, num_groups: Optional[int] = None,
                  max_seqs_per_group: int = 64, max_prefill_tokens: int = 2048, max_model_len: int = 32768,
-                 prefix_cache: bool = False, mixed_batches: bool = False):
+                 prefix_cache: bool = False, mixed_batches: bool = False, num_state_slots: Optional[int] = None):
         self.pipe = pipeline
         self.page_size = page_size
         self.num_groups = num_groups or max(1, getattr(pipeline, "num_stages", 1))
@@ -129,7 +129,13 @@ class LLMEngine:
         # mixed_batches: a prefill step also carries the next decode token of every running sequence of the group (one ragged
         # batch), so streams in flight keep their inter-token latency while new prompts are being prefilled
         self.mixed_batches = mixed_batches
-        self.table = SequenceTable(PageAllocator(num_pages), page_size)
+        # models with recurrent layers keep a state slot per live sequence (engine/kv_cache.py::HybridCache); the pipeline's cache says
+        # how many it has
+        if num_state_slots is None:
+            num_state_slots = getattr(pipeline, "num_state_slots", 0)
+        self.table = SequenceTable(PageAllocator(num_pages), page_size, SlotAllocator(num_state_slots) if num_state_slots else None)
+        if self.table.slots is not None and prefix_cache:
+            raise ValueError("prefix caching shares pages, not recurrent state: not available for models with state slots")
         # automatic prefix caching (engine/kv_cache.py::PrefixCache): full prompt pages are shared between requests
         self.table.prefix = PrefixCache(self.table.alloc, page_size) if prefix_cache else None
         self.waiting: "queue.Queue[Request]" = queue.Queue()
@@ -257,7 +263,7 @@ class LLMEngine:
             cache = self.table.prefix
             shared = cache.match(r.prompt) if cache is not None else []
             need = (len(r.prompt) + r.max_tokens + self.page_size - 1) // self.page_size - len(shared)
-            if need > self.table.alloc.num_free:
+            if need > self.table.alloc.num_free or (self.table.slots is not None and not self.table.slots.num_free):
                 if shared:
                     cache.release(shared)   # give the references back; the request is retried later
                 if not any(self.groups):
@@ -319,7 +325,8 @@ class LLMEngine:
         bts = [self.table.pages[r.id] for r in seqs]
         # block-table width rounded up to a multiple of 8 so captured decode graphs (graph_decode.py) are reused
         width = (max(len(p) for p in bts) + 7) // 8 * 8
-        meta = BatchMeta.build(q_lens, ctx0, bts, self.page_size, pad_blocks_to=width)
+        meta = BatchMeta.build(q_lens, ctx0, bts, self.page_size, pad_blocks_to=width,
+                               state_slots=self.table.state_slots([r.id for r in seqs]))
         ctxs = [(r.prompt + r.output)[-max(1, r.params.repetition_context_size):]
                 if r.params.repetition_penalty not in (0, 1.0) else [] for r in seqs]
         return StepInput(g, [r.id for r in seqs], torch.tensor(toks, dtype=torch.int64), meta,

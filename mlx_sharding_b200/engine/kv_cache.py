@@ -149,24 +149,82 @@ class PagedKVCache:
         return num_layers * page_size * kv_heads * (d_k + d_v) * itemsize
 
     @classmethod
-    def for_model(cls, model, num_pages: int, page_size: int = 64):
+    def for_model(cls, model, num_pages: int, page_size: int = 64, num_slots: int = 0):
+        if hasattr(model, "cache_layout"):     # hybrid stack: per-layer pools / state slots (``HybridCache``)
+            return HybridCache(model.cache_layout(), num_pages, page_size, max(2, num_slots or 65), model.device)
         L, hk, dk, dv = model.kv_geometry()
         return cls(L, num_pages, page_size, hk, dk, dv, model.dtype, model.device)
 
 
-class SequenceTable:
-    """Host-side block tables: sequence id -> (pages, length)."""
+class SlotAllocator:
+    """Free list of recurrent-state slots; slot 0 is the null slot (padding rows of a decode batch read / write it).  A slot is
+    handed out dirty: the kernels start a sequence whose step begins at position 0 from a zero state, so re-use needs no clear."""
 
-    def __init__(self, allocator: PageAllocator, page_size: int):
+    def __init__(self, num_slots: int):
+        if num_slots < 2:
+            raise ValueError("need at least 2 state slots (slot 0 is reserved)")
+        self.num_slots = num_slots
+        self._free: List[int] = list(range(num_slots - 1, 0, -1))
+
+    @property
+    def num_free(self) -> int:
+        return len(self._free)
+
+    def alloc(self) -> int:
+        if not self._free:
+            raise MemoryError("no free recurrent-state slot")
+        return self._free.pop()
+
+    def free(self, slot: int):
+        self._free.append(slot)
+
+
+class HybridCache(PagedKVCache):
+    """Cache of a model whose layers keep different things between steps: paged pools for attention layers (any row width, one
+    pool per layer: ``k[li]``; ``v[li]`` is an empty tensor when the values are read out of the key rows) and per-sequence *state
+    slots* for recurrent layers (``state[li]`` = dict name -> ``[num_slots, ...]`` tensor).  ``layout`` lists the local layers:
+    ``("paged", row_width, dtype)`` or ``("state", {name: (shape, dtype)})``.  Pages and slots are managed on the host by
+    :class:`SequenceTable`; the step metadata carries block tables and slot ids."""
+
+    def __init__(self, layout, num_pages: int, page_size: int, num_slots: int, device="cpu"):
+        self.num_layers, self.num_pages, self.page_size, self.num_slots = len(layout), num_pages, page_size, num_slots
+        self.kv_heads, self.d_k, self.d_v = 1, 0, 0
+        self.k, self.v, self.state = [], [], []
+        for ent in layout:
+            if ent[0] == "paged":
+                self.k.append(torch.zeros(num_pages, 1, page_size, ent[1], dtype=ent[2], device=device))
+                self.v.append(torch.empty(0, dtype=ent[2], device=device))
+                self.state.append(None)
+            else:
+                self.k.append(None)
+                self.v.append(None)
+                self.state.append({n: torch.zeros(num_slots, *shape, dtype=dt, device=device) for n, (shape, dt) in ent[1].items()})
+
+    def nbytes(self) -> int:
+        ts = [t for t in self.k if t is not None] + [t for d in self.state if d for t in d.values()]
+        return sum(t.numel() * t.element_size() for t in ts)
+
+
+class SequenceTable:
+    """Host-side block tables: sequence id -> (pages, length) and, for models with recurrent layers, its state slot."""
+
+    def __init__(self, allocator: PageAllocator, page_size: int, slots: Optional[SlotAllocator] = None):
         self.alloc = allocator
         self.page_size = page_size
         self.pages: Dict[int, List[int]] = {}
         self.length: Dict[int, int] = {}
         self.prefix: Optional[PrefixCache] = None
+        self.slots = slots
+        self.slot: Dict[int, int] = {}
 
     def add(self, seq_id: int):
+        if self.slots is not None:
+            self.slot[seq_id] = self.slots.alloc()
         self.pages[seq_id] = []
         self.length[seq_id] = 0
+
+    def state_slots(self, seq_ids) -> Optional[List[int]]:
+        return None if self.slots is None else [self.slot[s] for s in seq_ids]
 
     def reserve(self, seq_id: int, new_tokens: int):
         """Make sure pages exist for ``new_tokens`` more positions (does not advance the length)."""
@@ -185,6 +243,8 @@ class SequenceTable:
             pages = self.pages.pop(seq_id)
             self.alloc.free(self.prefix.release(pages) if self.prefix is not None else pages)
             self.length.pop(seq_id, None)
+            if seq_id in self.slot:
+                self.slots.free(self.slot.pop(seq_id))
 
     def release_all(self):
         for s in list(self.pages):

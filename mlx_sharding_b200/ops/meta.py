@@ -12,7 +12,7 @@ stage-to-stage hand-off in front of the hidden-state payload.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import List, Sequence
+from typing import List, Optional, Sequence
 
 import numpy as np
 import torch
@@ -32,6 +32,7 @@ class BatchMeta:
     max_ctx_len: int
     page_size: int
     fresh: bool = False          # host-side hint: no sequence of this step has cached context (every prompt starts at position 0)
+    state_slots: Optional[torch.Tensor] = None   # int32 [B] recurrent-state slot of each sequence (slot 0 = the null slot)
 
     @property
     def is_decode(self) -> bool:
@@ -41,7 +42,8 @@ class BatchMeta:
         mv = lambda t: t.to(device, non_blocking=non_blocking)
         return BatchMeta(mv(self.positions), mv(self.slot_mapping), mv(self.cu_seqlens), mv(self.context_lens),
                          mv(self.block_tables), mv(self.last_idx), self.num_tokens, self.num_seqs,
-                         self.max_q_len, self.max_ctx_len, self.page_size, self.fresh)
+                         self.max_q_len, self.max_ctx_len, self.page_size, self.fresh,
+                         None if self.state_slots is None else mv(self.state_slots))
 
     # ------------------------------------------------------------------ wire format
     def pack(self) -> torch.Tensor:
@@ -50,12 +52,13 @@ class BatchMeta:
         head = torch.tensor([T, B, self.max_q_len, self.max_ctx_len, self.page_size, mb], dtype=torch.int32)
         parts = [head, self.positions.cpu().int(), self.slot_mapping.cpu().int(), self.cu_seqlens.cpu().int(),
                  self.context_lens.cpu().int(), self.last_idx.cpu().int(),
-                 self.block_tables.cpu().int().reshape(-1)]
+                 self.block_tables.cpu().int().reshape(-1),
+                 torch.zeros(B, dtype=torch.int32) if self.state_slots is None else self.state_slots.cpu().int()]
         return torch.cat(parts)
 
     @staticmethod
     def packed_size(T: int, B: int, max_blocks: int) -> int:
-        return 6 + 2 * T + (B + 1) + 2 * B + B * max_blocks
+        return 6 + 2 * T + (B + 1) + 3 * B + B * max_blocks
 
     @staticmethod
     def unpack(buf: torch.Tensor) -> "BatchMeta":
@@ -70,14 +73,20 @@ class BatchMeta:
         positions, slots = take(T), take(T)
         cu, ctx, last = take(B + 1), take(B), take(B)
         bt = take(B * mb).reshape(B, mb)
-        return BatchMeta(positions, slots, cu, ctx, bt, last, T, B, mq, mc, ps)
+        ss = take(B)
+        return BatchMeta(positions, slots, cu, ctx, bt, last, T, B, mq, mc, ps, state_slots=ss)
 
     # ------------------------------------------------------------------ builders
     @staticmethod
     def build(q_lens: Sequence[int], ctx_before: Sequence[int], block_tables: Sequence[Sequence[int]],
-              page_size: int, device="cpu", pad_blocks_to: int = 0) -> "BatchMeta":
-        """Build from per-sequence query lengths, already-cached lengths and page lists."""
+              page_size: int, device="cpu", pad_blocks_to: int = 0, state_slots: Optional[Sequence[int]] = None) -> "BatchMeta":
+        """Build from per-sequence query lengths, already-cached lengths and page lists (and, for models with recurrent layers,
+        the state slot of each sequence)."""
         B = len(q_lens)
+        if state_slots is not None:
+            m = BatchMeta.build(q_lens, ctx_before, block_tables, page_size, "cpu", pad_blocks_to)
+            m.state_slots = torch.tensor([int(s) for s in state_slots], dtype=torch.int32)
+            return m.to(device) if str(device) != "cpu" else m
         if B and max(q_lens) == 1 and min(q_lens) == 1:
             # decode step: one token per sequence — no per-token inner loop (host fast path, once per generated token)
             pos = [int(c) for c in ctx_before]

@@ -318,3 +318,165 @@ def mla_rope_kv_write(q: torch.Tensor, k_pe: torch.Tensor, kv: torch.Tensor, kpo
     kp = k_pe.clone().unsqueeze(1)
     rope_(kp, meta.positions, spec, 0)
     kv_write_mla(kv, kp.squeeze(1), kpool, vpool, meta.slot_mapping, nope, vdim)
+
+
+# ------------------------------------------------------------------------------------------ hybrid-stack mechanisms
+# Unfused PyTorch forms of the ops behind recurrent / latent-attention layers (``ops/csrc/hybrid.cu`` on the CUDA backend).  All
+# take the ragged step metadata: rows ``cu_seqlens[b] .. cu_seqlens[b+1]`` belong to sequence ``b``, whose recurrent state lives in
+# slot ``meta.state_slots[b]``; a sequence whose step starts at position 0 starts from a zero state, whatever the slot holds.
+def _seq_ranges(meta: BatchMeta):
+    cu, ctx = meta.cu_seqlens.tolist(), meta.context_lens.tolist()
+    slots = meta.state_slots.tolist() if meta.state_slots is not None else [0] * meta.num_seqs
+    for b in range(meta.num_seqs):
+        yield cu[b], cu[b + 1], ctx[b] - (cu[b + 1] - cu[b]), slots[b]
+
+
+def gather_rows(table: torch.Tensor, ids: torch.Tensor, col0: int, ncols: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``out[t] = table[ids[t], col0:col0+ncols]`` (embedding lookup, optionally of a column block)."""
+    return table[ids.long(), col0:col0 + ncols].to(out_dtype)
+
+
+def post_norm_add_(x: torch.Tensor, y: torch.Tensor, w: torch.Tensor, eps: float, act_dtype: torch.dtype) -> torch.Tensor:
+    """Norm on the sublayer's OUTPUT: ``x += y / sqrt(mean(y^2) + eps) * w`` on the fp32 residual ``x`` (in place); returns ``x`` in
+    the activation dtype (``x`` itself when that is fp32) for the next projection."""
+    yf = y.float()
+    x += yf * torch.rsqrt(yf.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    return x if act_dtype == torch.float32 else x.to(act_dtype)
+
+
+def rmsnorm_cast(x: torch.Tensor, w: torch.Tensor, eps: float, out_dtype: torch.dtype) -> torch.Tensor:
+    xf = x.float()
+    return (xf * torch.rsqrt(xf.pow(2).mean(-1, keepdim=True) + eps) * w.float()).to(out_dtype)
+
+
+def gelu_erf_(x: torch.Tensor) -> torch.Tensor:
+    return x.copy_(F.gelu(x.float()).to(x.dtype))
+
+
+def side_gate(gx: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, col0: int) -> torch.Tensor:
+    """``gelu_tanh(gx) * table[ids, col0:col0+dim]`` (the gate of a per-layer token input)."""
+    e = table[ids.long(), col0:col0 + gx.shape[1]].float()
+    return (F.gelu(gx.float(), approximate="tanh") * e).to(gx.dtype)
+
+
+def causal_conv_silu(u: torch.Tensor, w: torch.Tensor, b: torch.Tensor, conv_state: torch.Tensor, meta: BatchMeta) -> torch.Tensor:
+    """Per-channel causal convolution + SiLU over a ragged batch.  ``u`` ``[T, C]`` (may be a column view), ``w`` ``[C, K]`` (last
+    column = current token), ``conv_state`` ``[slots, K-1, C]`` = the last ``K-1`` inputs of each sequence (updated here)."""
+    K = w.shape[1]
+    out = torch.empty(u.shape, dtype=u.dtype, device=u.device)
+    for s, e, c0, slot in _seq_ranges(meta):
+        hist = conv_state[slot].to(u.dtype) if c0 > 0 else torch.zeros(K - 1, u.shape[1], dtype=u.dtype, device=u.device)
+        full = torch.cat([hist, u[s:e]])
+        acc = b.float().expand(e - s, -1).clone()
+        for k in range(K):
+            acc += full[k:k + e - s].float() * w[:, k].float()
+        out[s:e] = F.silu(acc).to(u.dtype)
+        if K > 1:
+            conv_state[slot] = full[-(K - 1):].to(conv_state.dtype)
+    return out
+
+
+def ssm_scan(xbc: torch.Tensor, dt_raw: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor,
+             state: torch.Tensor, meta: BatchMeta, heads: int, vdim: int, nstate: int, groups: int) -> torch.Tensor:
+    """Selective state-space recurrence per head (fp32): ``S <- exp(-exp(A_log) dt) S + dt B x^T``, ``y = S^T C + D x`` with
+    ``dt = softplus(dt_raw + dt_bias)``.  ``xbc`` = ``[x: heads*vdim | B: groups*nstate | C: groups*nstate]`` after the convolution;
+    ``state`` ``[slots, heads, nstate, vdim]`` fp32.  Returns fp32 ``[T, heads*vdim]``."""
+    T, inner = xbc.shape[0], heads * vdim
+    y = torch.empty(T, heads, vdim, dtype=torch.float32, device=xbc.device)
+    x = xbc[:, :inner].float().view(T, heads, vdim)
+    rep = heads // groups
+    Bm = xbc[:, inner:inner + groups * nstate].float().view(T, groups, nstate).repeat_interleave(rep, 1)
+    Cm = xbc[:, inner + groups * nstate:].float().view(T, groups, nstate).repeat_interleave(rep, 1)
+    dt = F.softplus(dt_raw.float() + dt_bias.float(), threshold=80.0)
+    a = torch.exp(-torch.exp(A_log.float()) * dt)
+    for s, e, c0, slot in _seq_ranges(meta):
+        S = state[slot].clone() if c0 > 0 else torch.zeros_like(state[slot])
+        for t in range(s, e):
+            S = a[t, :, None, None] * S + (dt[t, :, None] * Bm[t])[:, :, None] * x[t][:, None, :]
+            y[t] = torch.einsum("hnp,hn->hp", S, Cm[t]) + D.float()[:, None] * x[t]
+        state[slot] = S
+    return y.view(T, inner)
+
+
+def decay_scan(qkv: torch.Tensor, decay: torch.Tensor, state: torch.Tensor, meta: BatchMeta, heads: int, dim: int, vdim: int) -> torch.Tensor:
+    """Linear attention with a constant per-head decay (fp32 state): ``S <- decay S + k v^T``, ``o = S^T q`` on
+    ``q, k, v = silu(.)`` of the columns ``[q: heads*dim | k: heads*dim | v: heads*vdim]``.  ``state`` ``[slots, heads, dim, vdim]``."""
+    T = qkv.shape[0]
+    act = F.silu(qkv[:, :2 * heads * dim + heads * vdim].float())
+    q, k = act[:, :heads * dim].view(T, heads, dim), act[:, heads * dim:2 * heads * dim].view(T, heads, dim)
+    v = act[:, 2 * heads * dim:].view(T, heads, vdim)
+    o = torch.empty(T, heads, vdim, dtype=torch.float32, device=qkv.device)
+    d = decay.float()[:, None, None]
+    for s, e, c0, slot in _seq_ranges(meta):
+        S = state[slot].clone() if c0 > 0 else torch.zeros_like(state[slot])
+        for t in range(s, e):
+            S = d * S + k[t][:, :, None] * v[t][:, None, :]
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t])
+        state[slot] = S
+    return o.view(T, heads * vdim)
+
+
+def gated_rmsnorm(y: torch.Tensor, gate: torch.Tensor, w: torch.Tensor, eps: float, groups: int, mode: str,
+                  out_dtype: torch.dtype) -> torch.Tensor:
+    """``mode='silu_pre'``: RMS norm in ``groups`` equal parts of ``y * silu(gate)``; ``mode='sigmoid_post'``: ``norm(y) * sigmoid(gate)``.
+    Both times ``w``; fp32 arithmetic."""
+    yf, g = y.float(), gate.float()
+    if mode == "silu_pre":
+        yf = yf * F.silu(g)
+    T, C = yf.shape
+    v = yf.view(T, groups, C // groups)
+    v = (v * torch.rsqrt(v.pow(2).mean(-1, keepdim=True) + eps)).view(T, C) * w.float()
+    if mode == "sigmoid_post":
+        v = v * torch.sigmoid(g)
+    return v.to(out_dtype)
+
+
+def _rot_half(v: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    half = inv_freq.numel()
+    a = pos.float()[:, None] * inv_freq.float()
+    c, s = torch.cos(a), torch.sin(a)
+    while c.dim() < v.dim():
+        c, s = c.unsqueeze(1), s.unsqueeze(1)
+    u1, u2 = v[..., :half], v[..., half:2 * half]
+    return torch.cat([u1 * c - u2 * s, u2 * c + u1 * s, v[..., 2 * half:]], -1)
+
+
+def latent_kv_prologue(dqkv: torch.Tensor, q_rank: int, kv_rank: int, qn_w: torch.Tensor, kvn_w: torch.Tensor, eps: float,
+                       pool: torch.Tensor, meta: BatchMeta, inv_freq: torch.Tensor) -> torch.Tensor:
+    """Rows ``[c_q raw: q_rank | c raw: kv_rank | k_rot raw]`` -> returns ``RMSnorm(c_q) * qn_w``; appends ``[RMSnorm(c) * kvn_w |
+    rotate_half(k_rot)]`` to the paged latent pool ``[pages, 1, page, kv_rank + rot]`` at ``meta.slot_mapping``."""
+    cq = rmsnorm_cast(dqkv[:, :q_rank], qn_w, eps, dqkv.dtype)
+    c = rmsnorm_cast(dqkv[:, q_rank:q_rank + kv_rank], kvn_w, eps, torch.float32)
+    kr = _rot_half(dqkv[:, q_rank + kv_rank:].float(), meta.positions, inv_freq)
+    flat = pool.view(-1, pool.shape[-1])
+    flat[meta.slot_mapping.long()] = torch.cat([c, kr], -1).to(pool.dtype)
+    return cq
+
+
+def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: torch.Tensor, meta: BatchMeta, scale: float, kv_rank: int,
+                     inv_freq: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+    """Causal multi-query attention over the cached latent rows with a *sink* in the softmax.  ``q`` ``[T, H, kv_rank + rot]`` (latent
+    part already multiplied by the key up-projection; the rot part is rotated here), keys = pool rows, values = their first
+    ``kv_rank`` entries; ``p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i))``.  Returns fp32 ``[T, H, kv_rank]``."""
+    T, H, Dq = q.shape
+    page = pool.shape[2]
+    qf = q.float()
+    qf = torch.cat([qf[..., :kv_rank], _rot_half(qf[..., kv_rank:], meta.positions, inv_freq)], -1)
+    out = torch.empty(T, H, kv_rank, dtype=torch.float32, device=q.device)
+    bt = meta.block_tables.long()
+    for b, (s, e, c0, _) in enumerate(_seq_ranges(meta)):
+        n = c0 + (e - s)
+        idx = torch.arange(n, device=q.device)
+        rows = pool.view(-1, Dq)[bt[b, idx // page] * page + idx % page].float()               # [n, Dq]
+        sc = torch.einsum("thd,nd->thn", qf[s:e], rows) * scale
+        mask = idx[None, :] > (c0 + torch.arange(e - s, device=q.device))[:, None]
+        sc = sc.masked_fill(mask[:, None, :], float("-inf"))
+        sk = sink.float().view(1, H, 1).expand(e - s, H, 1)
+        p = torch.softmax(torch.cat([sc, sk], -1), -1)[..., :n]
+        out[s:e] = torch.einsum("thn,nd->thd", p, rows[:, :kv_rank])
+    return out.to(out_dtype)
+
+
+def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x @ W^T`` for any shape / float dtype (fp32 accumulate)."""
+    return linear(x, W, out_dtype=out_dtype)

@@ -146,7 +146,8 @@ def _pad_decode(meta: BatchMeta, tokens: torch.Tensor, params, contexts, rng, Bp
     meta = BatchMeta(torch.cat([meta.positions, z(n)]), torch.cat([meta.slot_mapping, z(n)]), torch.arange(Bp + 1, dtype=torch.int32),
                      torch.cat([meta.context_lens, torch.ones(n, dtype=torch.int32)]),
                      torch.cat([meta.block_tables, torch.zeros(n, mb, dtype=torch.int32)]), torch.arange(Bp, dtype=torch.int32),
-                     Bp, Bp, 1, meta.max_ctx_len, meta.page_size)
+                     Bp, Bp, 1, meta.max_ctx_len, meta.page_size,
+                     state_slots=None if meta.state_slots is None else torch.cat([meta.state_slots, z(n)]))   # dummy rows: null slot
     tokens = torch.cat([tokens, torch.zeros(n, dtype=tokens.dtype)])
     params = list(params) + [_PAD_PARAMS] * n
     contexts = (list(contexts) + [[]] * n) if contexts is not None else None
@@ -239,7 +240,8 @@ class StepViews:
         ctx, o = take(B)
         last_idx, o = take(B)
         bt, o = take(B * mb)
-        self.meta = BatchMeta(pos, slots, cu, ctx, bt.view(B, mb), last_idx, T, B, max_q, max_ctx, page_size)
+        ss, o = take(B)
+        self.meta = BatchMeta(pos, slots, cu, ctx, bt.view(B, mb), last_idx, T, B, max_q, max_ctx, page_size, state_slots=ss)
         self.tokens = flat[lay.tokens:lay.tokens + 2 * T].view(torch.int64)
 
 

@@ -51,10 +51,10 @@ log = logging.getLogger(__name__)
 class StageExecutor:
     """A stage model + its paged KV pool (+ the host-parameter sampler used by the gRPC-compat relay)."""
 
-    def __init__(self, model, num_pages: int, page_size: int = 64, seed: int = 0):
+    def __init__(self, model, num_pages: int, page_size: int = 64, seed: int = 0, num_state_slots: int = 0):
         self.model = model
         self.device = model.device
-        self.kv = PagedKVCache.for_model(model, num_pages, page_size)
+        self.kv = PagedKVCache.for_model(model, num_pages, page_size, num_state_slots)
         self.sampler = Sampler(model.ops, self.device, seed) if model.spec.is_last else None
         from ..utils.tracing import StageTimer
 
@@ -205,6 +205,10 @@ class LocalPipeline:
         self.d2h_bytes = 0
         self._seq = 0
         self.gcache = self.runners[0].gcache if len(stages) == 1 else None
+
+    @property
+    def num_state_slots(self) -> int:
+        return getattr(self.stages[0].kv, "num_slots", 0)
 
     @property
     def h2d_bytes(self) -> int:

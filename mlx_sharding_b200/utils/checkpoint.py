@@ -95,6 +95,11 @@ def key_in_shard(key: str, spec: ShardSpec, tied_embeddings: bool = False, model
     """True if checkpoint tensor ``key`` belongs to stage ``spec`` (half-layer boundaries included)."""
     if "rotary_emb.inv_freq" in key:
         return False
+    if model_type == "perelorn":       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
+        m = re.match(r"l(\d+)\.", key)
+        if m:
+            return spec.owns_layer(int(m.group(1)))
+        return spec.is_last if key in ("final.norm", "head") else True
     m = _LAYER_RE.match(key)
     if m:
         i = int(m.group(1))
@@ -244,6 +249,9 @@ def random_state_dict(cfg: ModelConfig, spec: Optional[ShardSpec] = None, dtype=
     """
     spec = spec or cfg.shard()
     gen = torch.Generator(device=device)
+    if cfg.model_type == "perelorn":
+        yield from _perelorn_random(cfg, gen, dtype, device, seed)
+        return
     H = cfg.hidden_size
     q = quantization
     tied = cfg.tie_word_embeddings
@@ -325,6 +333,60 @@ def random_state_dict(cfg: ModelConfig, spec: Optional[ShardSpec] = None, dtype=
         yield from norm("model.norm", H, 7)
         if not tied:
             yield from lin("lm_head", cfg.vocab_size, H, 9)
+
+
+def _perelorn_random(cfg: ModelConfig, gen, dtype, device, seed: int):
+    """Random-init Perelorn tensors (checkpoint names and shapes of that design; decays / step sizes in a sane range)."""
+    gen.manual_seed(seed * 1000003 + 17)
+    W = cfg.hidden_size
+    rn = lambda *shape, std=1.0: torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std
+    lin = lambda o, i: (rn(o, i) / (i ** 0.5)).to(dtype)
+    vec = lambda n: (1.0 + 0.1 * rn(n)).to(dtype)
+    yield "embed", rn(cfg.vocab_size, W).to(dtype)
+    sd = cfg.token_side_dim
+    if sd:
+        yield "side.embed", rn(cfg.vocab_size, sd * cfg.num_hidden_layers).to(dtype)
+    for i, L in enumerate(cfg.layer_specs):
+        p, m = f"l{i}.", L["mixer"]
+        yield p + "norm1", vec(W)
+        if L["type"] == "mamba2":
+            H, P, N, G, K = m["heads"], m["vdim"], m["state"], m["groups"], m["conv"]
+            ch = H * P + 2 * G * N
+            yield p + "mix.in", lin(2 * H * P + 2 * G * N + H, W)
+            yield p + "mix.conv", (rn(ch, K) / (K ** 0.5)).to(dtype)
+            yield p + "mix.conv.b", rn(ch, std=0.1).to(dtype)
+            yield p + "mix.dt_bias", (rn(H) - 2.0).to(dtype)
+            yield p + "mix.A_log", (rn(H, std=0.5)).to(dtype)
+            yield p + "mix.D", vec(H)
+            yield p + "mix.norm", vec(H * P)
+            yield p + "mix.o", lin(W, H * P)
+        elif L["type"] == "lightning":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            for n, o in (("q", H * D), ("k", H * D), ("v", H * V), ("g", H * V)):
+                yield p + "mix." + n, lin(o, W)
+            yield p + "mix.o", lin(W, H * V)
+            yield p + "mix.norm", vec(H * V)
+        else:
+            H, D, R, V, Lr, Qr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"], m["q_rank"]
+            yield p + "mix.dq", lin(Qr, W)
+            yield p + "mix.dq.norm", vec(Qr)
+            yield p + "mix.uq", lin(H * (D + R), Qr)
+            yield p + "mix.dkv", lin(Lr + R, W)
+            yield p + "mix.dkv.norm", vec(Lr)
+            yield p + "mix.uk", lin(H * D, Lr)
+            yield p + "mix.uv", lin(H * V, Lr)
+            yield p + "mix.sink", rn(H).to(dtype)
+            yield p + "mix.o", lin(W, H * V)
+        if L["mlp"]:
+            yield p + "norm2", vec(W)
+            yield p + "mlp.up", lin(L["mlp"]["ff"], W)
+            yield p + "mlp.down", lin(W, L["mlp"]["ff"])
+        if sd:
+            yield p + "side.gate", lin(sd, W)
+            yield p + "side.proj", lin(W, sd)
+            yield p + "side.norm", vec(W)
+    yield "final.norm", vec(W)
+    yield "head", lin(cfg.vocab_size, W)
 
 
 def write_synthetic_checkpoint(path: str, config: Dict, dtype=torch.bfloat16, seed: int = 0,
