@@ -472,3 +472,76 @@ def mla_rope_kv_write(q, k_pe, kv, kpool, vpool, meta: BatchMeta, spec: RopeSpec
         raise NotImplementedError("fused MLA prologue expects interleaved (traditional) rope pairs")
     C().mla_rope_kv_write(q, k_pe, kv, kpool, vpool, meta.slot_mapping, meta.positions, spec.inv_freq, float(spec.mscale),
                           int(nope), int(vdim))
+
+
+# ------------------------------------------------------------------------------------------------ hybrid stacks (csrc/hybrid.cu)
+# Same functions as the unfused forms in ``ops/reference.py``.  Activations are bf16 (serving) or fp32 (exact mode: the kernels are
+# templated on the activation type; matrix products then go to cuBLAS in true fp32).
+def _is32(dt) -> bool:
+    if dt == torch.float32:
+        return True
+    if dt == torch.bfloat16:
+        return False
+    raise TypeError(f"b200 hybrid kernels take float32 / bfloat16 activations, got {dt}")
+
+
+def _slots(meta: BatchMeta) -> torch.Tensor:
+    if meta.state_slots is None:
+        raise ValueError("this step's metadata carries no state slots")
+    return meta.state_slots
+
+
+def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype) -> torch.Tensor:
+    """``x @ W^T``.  bf16 operands whose shapes fit the TMA rules (K and N multiples of 8, 16-byte aligned rows) take the tcgen05 GEMM;
+    fp32 operands (exact mode) and odd shapes go to cuBLAS."""
+    w = W.weight
+    if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.stride(1) == 1
+            and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] > 0):
+        return C().linear(x, w, None, None, None, 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+    y = torch.nn.functional.linear(x, w)
+    return y if y.dtype == out_dtype else y.to(out_dtype)
+
+
+def gather_rows(table, ids, col0: int, ncols: int, out_dtype):
+    return C().hy_gather_rows(table, ids, int(col0), int(ncols), _is32(out_dtype))
+
+
+def side_gate(gx, table, ids, col0: int):
+    return C().hy_side_gate(gx, table, ids, int(col0))
+
+
+def gelu_erf_(x):
+    return C().hy_gelu_erf_(x)
+
+
+def post_norm_add_(x, y, w, eps: float, act_dtype):
+    return C().hy_post_norm_add_(x, y, w, float(eps), _is32(act_dtype))
+
+
+def rmsnorm_cast(x, w, eps: float, out_dtype):
+    return C().hy_rmsnorm_cast(x, w, float(eps), _is32(out_dtype))
+
+
+def gated_rmsnorm(y, gate, w, eps: float, groups: int, mode: str, out_dtype):
+    return C().hy_gated_rmsnorm(y, gate, w, float(eps), int(groups), {"silu_pre": 0, "sigmoid_post": 1}[mode], _is32(out_dtype))
+
+
+def causal_conv_silu(u, w, b, conv_state, meta: BatchMeta):
+    return C().hy_causal_conv_silu(u, w, b, conv_state, meta.cu_seqlens, meta.context_lens, _slots(meta))
+
+
+def ssm_scan(xbc, dt_raw, dt_bias, A_log, D, state, meta: BatchMeta, heads: int, vdim: int, nstate: int, groups: int):
+    return C().hy_ssm_scan(xbc, dt_raw, dt_bias, A_log, D, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(vdim),
+                           int(nstate), int(groups))
+
+
+def decay_scan(qkv, decay, state, meta: BatchMeta, heads: int, dim: int, vdim: int):
+    return C().hy_decay_scan(qkv, decay, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(dim), int(vdim))
+
+
+def latent_kv_prologue(dqkv, q_rank: int, kv_rank: int, qn_w, kvn_w, eps: float, pool, meta: BatchMeta, inv_freq):
+    return C().hy_latent_prologue(dqkv, int(q_rank), int(kv_rank), qn_w, kvn_w, float(eps), pool, meta.slot_mapping, meta.positions, inv_freq)
+
+
+def latent_attention(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None):
+    return C().hy_latent_attention(q, pool, sink, meta.block_tables, meta.positions, meta.cu_seqlens, float(scale), int(kv_rank), inv_freq)

@@ -10,6 +10,7 @@
 
 #include "gemm_tcgen05.h"
 #include "kernels.h"
+#include "hybrid.h"
 
 namespace py = pybind11;
 using torch::Tensor;
@@ -796,6 +797,152 @@ Tensor ep_combine(int64_t flag_ptr, const Tensor& expected, int64_t error_ptr, c
 }
 }  // namespace
 
+// ---- hybrid stacks (hybrid.cu) --------------------------------------------------------------------------------------
+namespace {
+bool is_f32(const Tensor& t) { return t.scalar_type() == torch::kFloat32; }
+void check_act(const Tensor& t, const char* n) {
+  TORCH_CHECK(t.is_cuda() && (t.scalar_type() == torch::kFloat32 || t.scalar_type() == torch::kBFloat16), n, " must be a CUDA float32 / bfloat16 tensor");
+}
+void check_f32c(const Tensor& t, const char* n) { TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kFloat32 && t.is_contiguous(), n, " must be contiguous float32"); }
+void check_i32(const Tensor& t, const char* n) { TORCH_CHECK(t.is_cuda() && t.scalar_type() == torch::kInt32 && t.is_contiguous(), n, " must be contiguous int32"); }
+torch::ScalarType act_type(bool f32) { return f32 ? torch::kFloat32 : torch::kBFloat16; }
+}  // namespace
+
+Tensor hy_gather_rows(const Tensor& table, const Tensor& ids, int64_t col0, int64_t n, bool out_f32) {
+  check_act(table, "table"); check_rows(table, "table");
+  TORCH_CHECK(ids.is_cuda() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && col0 >= 0 && col0 + n <= table.size(1));
+  const c10::cuda::CUDAGuard guard(table.device());
+  Tensor out = torch::empty({ids.numel(), n}, table.options().dtype(act_type(out_f32)));
+  if (ids.numel() == 0) return out;
+  LAUNCH_OK(b200::gather_rows_launch(table.data_ptr(), is_f32(table), table.stride(0), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), (int)col0, (int)n, out.data_ptr(),
+                                     out_f32, (int)ids.numel(), cur_stream()));
+  return out;
+}
+
+Tensor hy_side_gate(const Tensor& gx, const Tensor& table, const Tensor& ids, int64_t col0) {
+  check_act(gx, "gx"); check_rows(gx, "gx"); check_rows(table, "table");
+  TORCH_CHECK(table.scalar_type() == gx.scalar_type() && ids.scalar_type() == torch::kInt64 && ids.is_contiguous() && col0 + gx.size(1) <= table.size(1));
+  const c10::cuda::CUDAGuard guard(gx.device());
+  Tensor out = torch::empty({gx.size(0), gx.size(1)}, gx.options());
+  LAUNCH_OK(b200::side_gate_launch(gx.data_ptr(), gx.stride(0), table.data_ptr(), table.stride(0), reinterpret_cast<const long long*>(ids.data_ptr<int64_t>()), (int)col0, (int)gx.size(1),
+                                   out.data_ptr(), is_f32(gx), (int)gx.size(0), cur_stream()));
+  return out;
+}
+
+Tensor hy_gelu_erf_(Tensor x) {
+  check_act(x, "x"); check_rows(x, "x");
+  const c10::cuda::CUDAGuard guard(x.device());
+  LAUNCH_OK(b200::gelu_erf_launch(x.data_ptr(), x.stride(0), (int)x.size(1), is_f32(x), (int)x.size(0), cur_stream()));
+  return x;
+}
+
+Tensor hy_post_norm_add_(Tensor x, const Tensor& y, const Tensor& w, double eps, bool act_f32) {
+  check_f32c(x, "x"); check_f32c(w, "w"); check_rows(y, "y");
+  TORCH_CHECK(y.is_cuda() && y.scalar_type() == torch::kFloat32 && x.dim() == 2 && y.size(0) == x.size(0) && y.size(1) == x.size(1) && w.numel() == x.size(1));
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor xa = act_f32 ? x : torch::empty({x.size(0), x.size(1)}, x.options().dtype(torch::kBFloat16));
+  LAUNCH_OK(b200::post_norm_add_launch(x.data_ptr<float>(), y.data_ptr<float>(), y.stride(0), w.data_ptr<float>(), act_f32 ? nullptr : xa.data_ptr(),
+                                       act_f32, (int)x.size(1), (float)eps, (int)x.size(0), cur_stream()));
+  return xa;
+}
+
+Tensor hy_rmsnorm_cast(const Tensor& x, const Tensor& w, double eps, bool out_f32) {
+  check_rows(x, "x"); check_f32c(w, "w");
+  TORCH_CHECK(x.is_cuda() && x.scalar_type() == torch::kFloat32 && w.numel() == x.size(1));
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor out = torch::empty({x.size(0), x.size(1)}, x.options().dtype(act_type(out_f32)));
+  if (x.size(0) == 0) return out;
+  LAUNCH_OK(b200::rmsnorm_cast_launch(x.data_ptr<float>(), x.stride(0), w.data_ptr<float>(), out.data_ptr(), out_f32, (int)x.size(1), (float)eps,
+                                      (int)x.size(0), cur_stream()));
+  return out;
+}
+
+Tensor hy_gated_rmsnorm(const Tensor& y, const Tensor& g, const Tensor& w, double eps, int64_t groups, int64_t mode, bool out_f32) {
+  check_f32c(y, "y"); check_f32c(w, "w"); check_act(g, "gate"); check_rows(g, "gate");
+  TORCH_CHECK(is_f32(g) == out_f32 && g.size(0) == y.size(0) && g.size(1) == y.size(1) && w.numel() == y.size(1) && groups >= 1 && y.size(1) % groups == 0);
+  const c10::cuda::CUDAGuard guard(y.device());
+  Tensor out = torch::empty({y.size(0), y.size(1)}, y.options().dtype(act_type(out_f32)));
+  LAUNCH_OK(b200::gated_rmsnorm_launch(y.data_ptr<float>(), g.data_ptr(), g.stride(0), w.data_ptr<float>(), out.data_ptr(), out_f32, (int)y.size(1),
+                                       (int)groups, (int)mode, (float)eps, (int)y.size(0), cur_stream()));
+  return out;
+}
+
+Tensor hy_causal_conv_silu(const Tensor& u, const Tensor& w, const Tensor& bias, Tensor cstate, const Tensor& cu, const Tensor& ctx,
+                           const Tensor& slots) {
+  check_act(u, "u"); check_rows(u, "u"); check_f32c(w, "w"); check_f32c(bias, "bias"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens");
+  check_i32(slots, "state_slots");
+  const int64_t T = u.size(0), C = u.size(1), K = w.size(1), B = slots.numel();
+  TORCH_CHECK(w.size(0) == C && bias.numel() == C && cstate.is_contiguous() && cstate.scalar_type() == u.scalar_type() && cu.numel() == B + 1);
+  TORCH_CHECK(K == 1 || (cstate.dim() == 3 && cstate.size(1) == K - 1 && cstate.size(2) == C), "conv state must be [slots, taps - 1, channels]");
+  TORCH_CHECK(K <= 17, "short convolution: at most 17 taps");
+  const c10::cuda::CUDAGuard guard(u.device());
+  Tensor out = torch::empty({T, C}, u.options());
+  LAUNCH_OK(b200::causal_conv_silu_launch(u.data_ptr(), u.stride(0), w.data_ptr<float>(), bias.data_ptr<float>(), cstate.data_ptr(), cu.data_ptr<int>(),
+                                          ctx.data_ptr<int>(), slots.data_ptr<int>(), (int)B, (int)C, (int)K, out.data_ptr(), is_f32(u), (int)T, cur_stream()));
+  return out;
+}
+
+Tensor hy_ssm_scan(const Tensor& xbc, const Tensor& dt, const Tensor& dt_bias, const Tensor& A_log, const Tensor& D, Tensor state, const Tensor& cu,
+                   const Tensor& ctx, const Tensor& slots, int64_t H, int64_t P, int64_t N, int64_t G) {
+  check_act(xbc, "xbc"); check_rows(xbc, "xbc"); check_rows(dt, "dt"); check_f32c(dt_bias, "dt_bias"); check_f32c(A_log, "A_log"); check_f32c(D, "D");
+  check_f32c(state, "state"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens"); check_i32(slots, "state_slots");
+  TORCH_CHECK(dt.scalar_type() == xbc.scalar_type() && xbc.size(1) == H * P + 2 * G * N && dt.size(1) == H && H % G == 0 && P <= 1024);
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == N && state.size(3) == P && dt_bias.numel() == H && A_log.numel() == H && D.numel() == H);
+  const c10::cuda::CUDAGuard guard(xbc.device());
+  Tensor out = torch::empty({xbc.size(0), H * P}, xbc.options().dtype(torch::kFloat32));
+  LAUNCH_OK(b200::ssm_scan_launch(xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr<float>(), A_log.data_ptr<float>(),
+                                  D.data_ptr<float>(), state.data_ptr<float>(), cu.data_ptr<int>(), ctx.data_ptr<int>(), slots.data_ptr<int>(),
+                                  out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)N, (int)P, (int)G, is_f32(xbc), cur_stream()));
+  return out;
+}
+
+Tensor hy_decay_scan(const Tensor& qkv, const Tensor& decay, Tensor state, const Tensor& cu, const Tensor& ctx, const Tensor& slots, int64_t H,
+                     int64_t Dk, int64_t V) {
+  check_act(qkv, "qkv"); check_rows(qkv, "qkv"); check_f32c(decay, "decay"); check_f32c(state, "state");
+  check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens"); check_i32(slots, "state_slots");
+  TORCH_CHECK(qkv.size(1) >= 2 * H * Dk + H * V && decay.numel() == H && V <= 1024);
+  TORCH_CHECK(state.dim() == 4 && state.size(1) == H && state.size(2) == Dk && state.size(3) == V);
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor out = torch::empty({qkv.size(0), H * V}, qkv.options().dtype(torch::kFloat32));
+  LAUNCH_OK(b200::decay_scan_launch(qkv.data_ptr(), qkv.stride(0), decay.data_ptr<float>(), state.data_ptr<float>(), cu.data_ptr<int>(),
+                                    ctx.data_ptr<int>(), slots.data_ptr<int>(), out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)Dk, (int)V,
+                                    is_f32(qkv), cur_stream()));
+  return out;
+}
+
+Tensor hy_latent_prologue(const Tensor& x, int64_t Qr, int64_t L, const Tensor& qn_w, const Tensor& kvn_w, double eps, Tensor pool,
+                          const Tensor& slot_map, const Tensor& positions, const Tensor& inv_freq) {
+  check_act(x, "x"); check_rows(x, "x"); check_f32c(qn_w, "qn_w"); check_f32c(kvn_w, "kvn_w"); check_f32c(inv_freq, "inv_freq");
+  check_i32(slot_map, "slot_mapping"); check_i32(positions, "positions");
+  const int64_t R = x.size(1) - Qr - L;
+  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && qn_w.numel() == Qr && kvn_w.numel() == L);
+  TORCH_CHECK(pool.is_contiguous() && pool.scalar_type() == x.scalar_type() && pool.size(-1) == L + R, "latent pool must be [..., kv_rank + rot] of the activation type");
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor cq = torch::empty({x.size(0), Qr}, x.options());
+  LAUNCH_OK(b200::latent_prologue_launch(x.data_ptr(), x.stride(0), (int)Qr, (int)L, (int)R, qn_w.data_ptr<float>(), kvn_w.data_ptr<float>(), (float)eps,
+                                         cq.data_ptr(), pool.data_ptr(), slot_map.data_ptr<int>(), positions.data_ptr<int>(), inv_freq.data_ptr<float>(),
+                                         is_f32(x), (int)x.size(0), cur_stream()));
+  return cq;
+}
+
+Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& sink, const Tensor& block_tables, const Tensor& positions,
+                           const Tensor& cu, double scale, int64_t L, const Tensor& inv_freq) {
+  check_act(q, "q"); check_f32c(sink, "sink"); check_f32c(inv_freq, "inv_freq"); check_i32(block_tables, "block_tables");
+  check_i32(positions, "positions"); check_i32(cu, "cu_seqlens");
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && pool.is_contiguous() && pool.dim() == 4 && pool.size(1) == 1 && pool.size(3) == q.size(2) &&
+              pool.scalar_type() == q.scalar_type(), "q [T, H, kv_rank + rot], pool [pages, 1, page, kv_rank + rot]");
+  const int64_t T = q.size(0), H = q.size(1), R = q.size(2) - L;
+  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && sink.numel() == H && L <= 512, "latent attention: kv_rank <= 512");
+  const c10::cuda::CUDAGuard guard(q.device());
+  Tensor out = torch::empty({T, H, L}, q.options());
+  if (T == 0) return out;
+  LAUNCH_OK(b200::latent_attention_launch(q.data_ptr(), pool.data_ptr(), sink.data_ptr<float>(), block_tables.data_ptr<int>(), (int)block_tables.size(1),
+                                          positions.data_ptr<int>(), cu.data_ptr<int>(), (int)(cu.numel() - 1), (int)H, (int)L, (int)R, (int)pool.size(2),
+                                          (float)scale, inv_freq.data_ptr<float>(), out.data_ptr(), is_f32(q), (int)T, cur_stream()));
+  return out;
+}
+
+
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mlx_sharding_b200 sm_100a kernels";
   m.def("linear", &linear, py::arg("x"), py::arg("w"), py::arg("w2") = py::none(), py::arg("residual") = py::none(),
@@ -868,6 +1015,17 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("ret_expected") = py::none(), py::arg("norm_w") = py::none(), py::arg("norm_eps") = 1e-6, py::arg("normed_out") = py::none());
   m.def("init_scratch", &init_scratch);
   m.def("launch_count", []() { return g_launches; });
+  m.def("hy_gather_rows", &hy_gather_rows);
+  m.def("hy_side_gate", &hy_side_gate);
+  m.def("hy_gelu_erf_", &hy_gelu_erf_);
+  m.def("hy_post_norm_add_", &hy_post_norm_add_);
+  m.def("hy_rmsnorm_cast", &hy_rmsnorm_cast);
+  m.def("hy_gated_rmsnorm", &hy_gated_rmsnorm);
+  m.def("hy_causal_conv_silu", &hy_causal_conv_silu);
+  m.def("hy_ssm_scan", &hy_ssm_scan);
+  m.def("hy_decay_scan", &hy_decay_scan);
+  m.def("hy_latent_prologue", &hy_latent_prologue);
+  m.def("hy_latent_attention", &hy_latent_attention);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });
   m.def("sm_arch", []() { return std::string("sm_100a"); });
 }

@@ -1,0 +1,487 @@
+// Kernels of hybrid decoder stacks: recurrent mixers (selective state-space scan, decayed linear attention), the short causal
+// convolution in front of them, gated / grouped RMS norms, output-side ("post") norm fused with the fp32 residual add, latent
+// multi-query attention with a softmax sink over a paged latent pool, and the small gathers around them.
+//
+// Conventions: a step is a ragged batch (rows cu_seqlens[b] .. cu_seqlens[b+1] belong to sequence b, whose first row sits at
+// position context_lens[b] - q_len); recurrent state lives in per-sequence slots and a sequence whose step starts at position 0
+// starts from a zero state whatever its slot holds, so slots are re-used without a clear.  Activations are AT = bf16 (serving) or
+// float (exact mode); the residual stream, norms, softmax and every recurrence are fp32 in both.
+#include "hybrid.h"
+
+#include <cuda_bf16.h>
+#include <math.h>
+
+namespace b200 {
+namespace {
+
+template <typename T> __device__ __forceinline__ float ldf(const T* p);
+template <> __device__ __forceinline__ float ldf<float>(const float* p) { return *p; }
+template <> __device__ __forceinline__ float ldf<__nv_bfloat16>(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+template <typename T> __device__ __forceinline__ void stf(T* p, float v);
+template <> __device__ __forceinline__ void stf<float>(float* p, float v) { *p = v; }
+template <> __device__ __forceinline__ void stf<__nv_bfloat16>(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+// activations round to AT between a projection and its nonlinearity, as an unfused graph does
+template <typename T> __device__ __forceinline__ float rnd(float v);
+template <> __device__ __forceinline__ float rnd<float>(float v) { return v; }
+template <> __device__ __forceinline__ float rnd<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
+
+__device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
+__device__ __forceinline__ float softplus_f(float v) { return v > 30.f ? v : log1pf(expf(v)); }
+__device__ __forceinline__ float gelu_tanh_f(float z) { return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z))); }
+__device__ __forceinline__ float gelu_erf_f(float z) { return 0.5f * z * (1.f + erff(z * 0.7071067811865476f)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+// sum over the block (blockDim.x <= 1024, multiple of 32); every thread gets the result
+__device__ __forceinline__ float block_sum(float v, float* red) {
+  v = warp_sum(v);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  __syncthreads();
+  if (l == 0) red[w] = v;
+  __syncthreads();
+  float t = l < nw ? red[l] : 0.f;
+  return warp_sum(t);
+}
+// sequence of row t: largest b with cu[b] <= t
+__device__ __forceinline__ int seq_of(const int* cu, int B, int t) {
+  int lo = 0, hi = B - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (cu[mid] <= t) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
+// ---------------------------------------------------------------------------------------------------------- gathers
+template <typename TT, typename OT>
+__global__ void gather_rows_kernel(const TT* __restrict__ table, long long ld, const long long* __restrict__ ids, int col0, int n,
+                                   OT* __restrict__ out) {
+  const long long row = ids[blockIdx.x];
+  const TT* src = table + row * ld + col0;
+  OT* dst = out + (long long)blockIdx.x * n;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) stf<OT>(dst + c, ldf<TT>(src + c));
+}
+
+template <typename AT>
+__global__ void side_gate_kernel(const AT* __restrict__ gx, long long ld_g, const AT* __restrict__ table, long long ld_t,
+                                 const long long* __restrict__ ids, int col0, int n, AT* __restrict__ out) {
+  const int t = blockIdx.x;
+  const AT* e = table + ids[t] * ld_t + col0;
+  for (int c = threadIdx.x; c < n; c += blockDim.x)
+    stf<AT>(out + (long long)t * n + c, rnd<AT>(gelu_tanh_f(ldf<AT>(gx + t * ld_g + c))) * ldf<AT>(e + c));
+}
+
+template <typename AT>
+__global__ void gelu_erf_kernel(AT* __restrict__ x, long long ld, int n) {
+  AT* row = x + (long long)blockIdx.x * ld;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) stf<AT>(row + c, gelu_erf_f(ldf<AT>(row + c)));
+}
+
+// ---------------------------------------------------------------------------------------------------------- norms
+// x += y * rsqrt(mean(y^2) + eps) * w  (x, y fp32);  xa = (AT) x  when xa != nullptr
+template <typename AT>
+__global__ void post_norm_add_kernel(float* __restrict__ x, const float* __restrict__ y, long long ld_y, const float* __restrict__ w,
+                                     AT* __restrict__ xa, int n, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const float* yr = y + t * ld_y;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = yr[c]; ss += v * v; }
+  const float r = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    const float v = x[t * n + c] + yr[c] * r * w[c];
+    x[t * n + c] = v;
+    if (xa != nullptr) stf<AT>(xa + t * n + c, v);
+  }
+}
+
+template <typename AT>
+__global__ void rmsnorm_cast_kernel(const float* __restrict__ x, long long ld_x, const float* __restrict__ w, AT* __restrict__ out, int n,
+                                    float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const float* xr = x + t * ld_x;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) { const float v = xr[c]; ss += v * v; }
+  const float r = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x) stf<AT>(out + t * n + c, xr[c] * r * w[c]);
+}
+
+// mode 0: norm_groups(y * silu(g)) * w      mode 1: norm(y) * w * sigmoid(g)        grid (T, groups)
+template <typename AT>
+__global__ void gated_rmsnorm_kernel(const float* __restrict__ y, const AT* __restrict__ g, long long ld_g, const float* __restrict__ w,
+                                     AT* __restrict__ out, int C, int groups, int mode, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const int gs = C / groups, c0 = blockIdx.y * gs;
+  const float* yr = y + t * C + c0;
+  const AT* gr = g + t * ld_g + c0;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    float v = yr[c];
+    if (mode == 0) v *= silu_f(ldf<AT>(gr + c));
+    ss += v * v;
+  }
+  const float r = rsqrtf(block_sum(ss, red) / (float)gs + eps);
+  for (int c = threadIdx.x; c < gs; c += blockDim.x) {
+    float v = yr[c];
+    const float gv = ldf<AT>(gr + c);
+    if (mode == 0) v *= silu_f(gv);
+    v = v * r * w[c0 + c];
+    if (mode == 1) v *= sigmoid_f(gv);
+    stf<AT>(out + t * C + c0 + c, v);
+  }
+}
+
+// ---------------------------------------------------------------------------------------------------------- short convolution
+// out[t, c] = silu(b[c] + sum_k w[c, k] * in(t - (K-1) + k, c)); inputs before this step come from the sequence's conv state
+// ([slots, K-1, C], the last K-1 inputs), inputs before position 0 are zero.          grid (T, ceil(C / blockDim))
+template <typename AT>
+__global__ void causal_conv_silu_kernel(const AT* __restrict__ u, long long ld_u, const float* __restrict__ w, const float* __restrict__ bias,
+                                        const AT* __restrict__ cstate, const int* __restrict__ cu, const int* __restrict__ ctx,
+                                        const int* __restrict__ slots, int B, int C, int K, AT* __restrict__ out) {
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int b = seq_of(cu, B, t);
+  const int j = t - cu[b], c0 = ctx[b] - (cu[b + 1] - cu[b]);
+  const AT* st = cstate + (long long)slots[b] * (K - 1) * C;
+  float acc = bias[c];
+  for (int k = 0; k < K; ++k) {
+    const int jj = j - (K - 1) + k;          // row of this step (>= 0) or history (< 0)
+    float v = 0.f;
+    if (jj >= 0) v = ldf<AT>(u + (long long)(t - j + jj) * ld_u + c);
+    else if (c0 > 0) v = ldf<AT>(st + (long long)(K - 1 + jj) * C + c);
+    acc += w[c * K + k] * v;
+  }
+  stf<AT>(out + (long long)t * C + c, silu_f(rnd<AT>(acc)));
+}
+
+// new state = last K-1 inputs of the sequence; each thread owns one (sequence, channel) column: reads, then writes
+template <typename AT>
+__global__ void conv_state_update_kernel(const AT* __restrict__ u, long long ld_u, AT* __restrict__ cstate, const int* __restrict__ cu,
+                                         const int* __restrict__ ctx, const int* __restrict__ slots, int C, int K) {
+  const int b = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int s = cu[b], q = cu[b + 1] - s, c0 = ctx[b] - q;
+  if (q == 0) return;
+  AT* st = cstate + (long long)slots[b] * (K - 1) * C;
+  float keep[16];
+  for (int i = 0; i < K - 1; ++i) {
+    const int jj = q - (K - 1) + i;
+    float v = 0.f;
+    if (jj >= 0) v = ldf<AT>(u + (long long)(s + jj) * ld_u + c);
+    else if (c0 > 0 && c0 + jj >= 0) v = ldf<AT>(st + (long long)(K - 1 + jj) * C + c);
+    keep[i] = v;
+  }
+  for (int i = 0; i < K - 1; ++i) stf<AT>(st + (long long)i * C + c, keep[i]);
+}
+
+// ---------------------------------------------------------------------------------------------------------- recurrent scans
+// One CTA per (sequence, head); state S[N][P] in shared memory (fp32), thread (r, p) owns rows n = r, r + R, ... of column p.
+//   MODE 0 (selective state space):  a_t = exp(-exp(A_log) dt_t), S <- a_t S + (dt_t B_t[n]) x_t[p], y_t[p] = sum_n S C_t[n] + D x_t[p]
+//   MODE 1 (decayed linear attention): S <- decay S + silu(k_t)[n] silu(v_t)[p], o_t[p] = sum_n S silu(q_t)[n]
+struct ScanArgs {
+  const void* in; long long ld_in;       // MODE 0: conv output [x | B | C];  MODE 1: projection [q | k | v | ...]
+  const void* dt; long long ld_dt;       // MODE 0: raw step sizes [T, H]
+  const float* dt_bias; const float* A_log; const float* D; const float* decay;
+  float* state;                          // [slots, H, N, P]
+  const int* cu; const int* ctx; const int* slots;
+  float* out;                            // fp32 [T, H * P]
+  int H, N, P, G;
+};
+
+template <typename AT, int MODE>
+__global__ void recurrent_scan_kernel(ScanArgs a) {
+  extern __shared__ float smem[];
+  const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H;
+  const int R = blockDim.x / P, p = threadIdx.x % P, r = threadIdx.x / P;
+  float* S = smem;                         // [N][P]
+  float* red = smem + N * P;               // [2][R][P]
+  const int s = a.cu[b], q = a.cu[b + 1] - s;
+  if (q == 0) return;
+  const bool fresh = a.ctx[b] - q == 0;
+  float* gs = a.state + ((long long)a.slots[b] * H + h) * N * P;
+  for (int i = threadIdx.x; i < N * P; i += blockDim.x) S[i] = fresh ? 0.f : gs[i];
+  __syncthreads();
+  const AT* in = reinterpret_cast<const AT*>(a.in);
+  const int g = MODE == 0 ? h / (H / a.G) : 0;
+  const float Aneg = MODE == 0 ? -expf(a.A_log[h]) : 0.f, Dh = MODE == 0 ? a.D[h] : 0.f, dtb = MODE == 0 ? a.dt_bias[h] : 0.f;
+  const float dec = MODE == 1 ? a.decay[h] : 0.f;
+  for (int j = 0; j < q; ++j) {
+    const AT* row = in + (long long)(s + j) * a.ld_in;
+    const AT *kp, *qp;
+    float decay, kscale, xv;
+    if (MODE == 0) {
+      const float dt = softplus_f(ldf<AT>(reinterpret_cast<const AT*>(a.dt) + (long long)(s + j) * a.ld_dt + h) + dtb);
+      decay = expf(Aneg * dt); kscale = dt;
+      xv = ldf<AT>(row + h * P + p);
+      kp = row + H * P + g * N; qp = row + H * P + a.G * N + g * N;
+    } else {
+      decay = dec; kscale = 1.f;
+      qp = row + h * N; kp = row + H * N + h * N;
+      xv = silu_f(ldf<AT>(row + 2 * H * N + h * P + p));
+    }
+    float acc = 0.f;
+    if (r < R) {
+      for (int n = r; n < N; n += R) {
+        float kv = ldf<AT>(kp + n), qv = ldf<AT>(qp + n);
+        if (MODE == 1) { kv = silu_f(kv); qv = silu_f(qv); }
+        const float sv = decay * S[n * P + p] + (kscale * kv) * xv;
+        S[n * P + p] = sv;
+        acc += sv * qv;
+      }
+      red[((j & 1) * R + r) * P + p] = acc;
+    }
+    __syncthreads();
+    if (r == 0) {
+      float y = 0.f;
+      for (int i = 0; i < R; ++i) y += red[((j & 1) * R + i) * P + p];
+      a.out[(long long)(s + j) * H * P + h * P + p] = y + Dh * xv;
+    }
+  }
+  __syncthreads();
+  for (int i = threadIdx.x; i < N * P; i += blockDim.x) gs[i] = S[i];
+}
+
+// ---------------------------------------------------------------------------------------------------------- latent attention
+// row [c_q raw: Qr | c raw: L | k_rot raw: R]  ->  cq = rms(c_q) * qn_w ;  pool[slot] = [rms(c) * kvn_w | rotate_half(k_rot, pos)]
+template <typename AT>
+__global__ void latent_prologue_kernel(const AT* __restrict__ x, long long ld_x, int Qr, int L, int R, const float* __restrict__ qn_w,
+                                       const float* __restrict__ kvn_w, float eps, AT* __restrict__ cq, AT* __restrict__ pool,
+                                       const int* __restrict__ slot_map, const int* __restrict__ positions, const float* __restrict__ inv_freq) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const AT* row = x + t * ld_x;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < Qr; c += blockDim.x) { const float v = ldf<AT>(row + c); ss += v * v; }
+  float r = rsqrtf(block_sum(ss, red) / (float)Qr + eps);
+  for (int c = threadIdx.x; c < Qr; c += blockDim.x) stf<AT>(cq + t * Qr + c, ldf<AT>(row + c) * r * qn_w[c]);
+  ss = 0.f;
+  for (int c = threadIdx.x; c < L; c += blockDim.x) { const float v = ldf<AT>(row + Qr + c); ss += v * v; }
+  r = rsqrtf(block_sum(ss, red) / (float)L + eps);
+  AT* dst = pool + (long long)slot_map[t] * (L + R);
+  for (int c = threadIdx.x; c < L; c += blockDim.x) stf<AT>(dst + c, ldf<AT>(row + Qr + c) * r * kvn_w[c]);
+  const float pos = (float)positions[t];
+  const int half = R / 2;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    float sn, cs;
+    sincosf(pos * inv_freq[i], &sn, &cs);
+    const float u = ldf<AT>(row + Qr + L + i), v = ldf<AT>(row + Qr + L + half + i);
+    stf<AT>(dst + L + i, u * cs - v * sn);
+    stf<AT>(dst + L + half + i, v * cs + u * sn);
+  }
+}
+
+// Causal multi-query attention over the paged latent rows, with a sink: softmax denominator = exp(sink_h) + sum_j exp(s_j).
+// grid (T, ceil(H / warps)); one warp per head; key tiles of 32 rows staged in shared memory as fp32 and shared by the heads.
+constexpr int kLatTile = 32;
+constexpr int kLatMaxPerLane = 16;   // latent width <= 512
+
+template <typename AT>
+__global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ pool, const float* __restrict__ sink,
+                                        const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ positions,
+                                        const int* __restrict__ cu, int B, int H, int L, int R, int page, float scale,
+                                        const float* __restrict__ inv_freq, AT* __restrict__ out) {
+  extern __shared__ float smem[];
+  const int Dq = L + R, ldk = Dq + 1, nw = blockDim.x >> 5;
+  float* qs = smem;                       // [nw][Dq]
+  float* ks = smem + nw * Dq;             // [tile][Dq + 1]
+  const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int h = blockIdx.y * nw + warp;
+  const int pos = positions[t];
+  const int b = seq_of(cu, B, t);
+  const int* bt = block_tables + (long long)b * max_blocks;
+  // queries of this block's heads -> smem (rot part rotated by the token's position)
+  const int half = R / 2;
+  for (int i = threadIdx.x; i < nw * Dq; i += blockDim.x) {
+    const int hh = blockIdx.y * nw + i / Dq, d = i % Dq;
+    float v = 0.f;
+    if (hh < H) {
+      const AT* qr = q + ((long long)t * H + hh) * Dq;
+      if (d < L) v = ldf<AT>(qr + d);
+      else {
+        const int e = d - L, f = e < half ? e : e - half;
+        float sn, cs;
+        sincosf((float)pos * inv_freq[f], &sn, &cs);
+        const float u = ldf<AT>(qr + L + f), w = ldf<AT>(qr + L + half + f);
+        v = rnd<AT>(e < half ? u * cs - w * sn : w * cs + u * sn);
+      }
+    }
+    qs[i] = v;
+  }
+  float m = h < H ? sink[h] : 0.f, l = 1.f;   // the sink: one extra term exp(sink - m), no key, no value
+  float o[kLatMaxPerLane];
+#pragma unroll
+  for (int i = 0; i < kLatMaxPerLane; ++i) o[i] = 0.f;
+  const int nper = (L + 31) / 32;
+  const float* qh = qs + warp * Dq;
+  for (int j0 = 0; j0 <= pos; j0 += kLatTile) {
+    __syncthreads();
+    const int nk = min(kLatTile, pos + 1 - j0);
+    for (int i = threadIdx.x; i < nk * Dq; i += blockDim.x) {
+      const int jj = i / Dq, d = i % Dq, j = j0 + jj;
+      ks[jj * ldk + d] = ldf<AT>(pool + ((long long)bt[j / page] * page + j % page) * Dq + d);
+    }
+    __syncthreads();
+    if (h >= H) continue;
+    float sc = -INFINITY;
+    if (lane < nk) {
+      const float* kr = ks + lane * ldk;
+      float acc = 0.f;
+      for (int d = 0; d < Dq; ++d) acc += qh[d] * kr[d];
+      sc = acc * scale;
+    }
+    const float mn = fmaxf(m, warp_max(sc));
+    const float corr = expf(m - mn), pj = lane < nk ? expf(sc - mn) : 0.f;
+    l = l * corr + warp_sum(pj);
+    m = mn;
+#pragma unroll
+    for (int i = 0; i < kLatMaxPerLane; ++i) o[i] *= corr;
+    for (int jj = 0; jj < nk; ++jj) {
+      const float pv = __shfl_sync(0xffffffffu, pj, jj);
+      const float* kr = ks + jj * ldk;
+#pragma unroll
+      for (int i = 0; i < kLatMaxPerLane; ++i)
+        if (i < nper) { const int d = lane + 32 * i; if (d < L) o[i] += pv * kr[d]; }
+    }
+  }
+  if (h < H) {
+    const float inv = 1.f / l;
+#pragma unroll
+    for (int i = 0; i < kLatMaxPerLane; ++i)
+      if (i < nper) { const int d = lane + 32 * i; if (d < L) stf<AT>(out + ((long long)t * H + h) * L + d, o[i] * inv); }
+  }
+}
+
+inline cudaError_t last() { return cudaGetLastError(); }
+#define AT_DISPATCH(f32, ...)                                      \
+  do {                                                             \
+    if (f32) { using AT = float; __VA_ARGS__; }                    \
+    else { using AT = __nv_bfloat16; __VA_ARGS__; }                \
+  } while (0)
+
+}  // namespace
+
+// ---------------------------------------------------------------------------------------------------------- launchers
+cudaError_t gather_rows_launch(const void* table, bool table_f32, long long ld, const long long* ids, int col0, int n, void* out,
+                               bool out_f32, int T, cudaStream_t s) {
+  const int th = n >= 256 ? 256 : 64;
+  if (table_f32 && out_f32) gather_rows_kernel<float, float><<<T, th, 0, s>>>((const float*)table, ld, ids, col0, n, (float*)out);
+  else if (table_f32) gather_rows_kernel<float, __nv_bfloat16><<<T, th, 0, s>>>((const float*)table, ld, ids, col0, n, (__nv_bfloat16*)out);
+  else if (out_f32) gather_rows_kernel<__nv_bfloat16, float><<<T, th, 0, s>>>((const __nv_bfloat16*)table, ld, ids, col0, n, (float*)out);
+  else gather_rows_kernel<__nv_bfloat16, __nv_bfloat16><<<T, th, 0, s>>>((const __nv_bfloat16*)table, ld, ids, col0, n, (__nv_bfloat16*)out);
+  return last();
+}
+
+cudaError_t side_gate_launch(const void* gx, long long ld_g, const void* table, long long ld_t, const long long* ids, int col0, int n,
+                             void* out, bool f32, int T, cudaStream_t s) {
+  AT_DISPATCH(f32, (side_gate_kernel<AT><<<T, 64, 0, s>>>((const AT*)gx, ld_g, (const AT*)table, ld_t, ids, col0, n, (AT*)out)));
+  return last();
+}
+
+cudaError_t gelu_erf_launch(void* x, long long ld, int n, bool f32, int T, cudaStream_t s) {
+  dim3 grid(T, (n + 1023) / 1024);
+  AT_DISPATCH(f32, (gelu_erf_kernel<AT><<<grid, 256, 0, s>>>((AT*)x, ld, n)));
+  return last();
+}
+
+cudaError_t post_norm_add_launch(float* x, const float* y, long long ld_y, const float* w, void* xa, bool f32, int n, float eps, int T,
+                                 cudaStream_t s) {
+  AT_DISPATCH(f32, (post_norm_add_kernel<AT><<<T, 256, 0, s>>>(x, y, ld_y, w, (AT*)xa, n, eps)));
+  return last();
+}
+
+cudaError_t rmsnorm_cast_launch(const float* x, long long ld_x, const float* w, void* out, bool f32, int n, float eps, int T,
+                                cudaStream_t s) {
+  AT_DISPATCH(f32, (rmsnorm_cast_kernel<AT><<<T, 256, 0, s>>>(x, ld_x, w, (AT*)out, n, eps)));
+  return last();
+}
+
+cudaError_t gated_rmsnorm_launch(const float* y, const void* g, long long ld_g, const float* w, void* out, bool f32, int C, int groups,
+                                 int mode, float eps, int T, cudaStream_t s) {
+  dim3 grid(T, groups);
+  AT_DISPATCH(f32, (gated_rmsnorm_kernel<AT><<<grid, 256, 0, s>>>(y, (const AT*)g, ld_g, w, (AT*)out, C, groups, mode, eps)));
+  return last();
+}
+
+cudaError_t causal_conv_silu_launch(const void* u, long long ld_u, const float* w, const float* bias, void* cstate, const int* cu,
+                                    const int* ctx, const int* slots, int B, int C, int K, void* out, bool f32, int T, cudaStream_t s) {
+  if (K - 1 > 16) return cudaErrorInvalidValue;
+  dim3 grid(T, (C + 255) / 256), gridu(B, (C + 255) / 256);
+  AT_DISPATCH(f32, (causal_conv_silu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)u, ld_u, w, bias, (const AT*)cstate, cu, ctx, slots, B, C, K,
+                                                                    (AT*)out)));
+  if (K > 1)
+    AT_DISPATCH(f32, (conv_state_update_kernel<AT><<<gridu, 256, 0, s>>>((const AT*)u, ld_u, (AT*)cstate, cu, ctx, slots, C, K)));
+  return last();
+}
+
+template <typename AT, int MODE>
+static cudaError_t scan_launch_t(const ScanArgs& a, int B, cudaStream_t s) {
+  const int P = a.P, N = a.N;
+  if (P > 1024) return cudaErrorInvalidValue;
+  int R = 256 / P;
+  if (R < 1) R = 1;
+  if (R > N) R = N;
+  int threads = (R * P + 31) / 32 * 32;         // the tail threads (r >= R) only help with the state copy
+  const size_t smem = ((size_t)N * P + 2 * (size_t)R * P) * sizeof(float);
+  auto k = recurrent_scan_kernel<AT, MODE>;
+  if (smem > 48 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return e;
+  }
+  k<<<dim3(B, a.H), threads, smem, s>>>(a);
+  return last();
+}
+
+cudaError_t ssm_scan_launch(const void* xbc, long long ld_x, const void* dt, long long ld_dt, const float* dt_bias, const float* A_log,
+                            const float* D, float* state, const int* cu, const int* ctx, const int* slots, float* out, int B, int H, int N,
+                            int P, int G, bool f32, cudaStream_t s) {
+  ScanArgs a{xbc, ld_x, dt, ld_dt, dt_bias, A_log, D, nullptr, state, cu, ctx, slots, out, H, N, P, G};
+  return f32 ? scan_launch_t<float, 0>(a, B, s) : scan_launch_t<__nv_bfloat16, 0>(a, B, s);
+}
+
+cudaError_t decay_scan_launch(const void* qkv, long long ld, const float* decay, float* state, const int* cu, const int* ctx,
+                              const int* slots, float* out, int B, int H, int N, int P, bool f32, cudaStream_t s) {
+  ScanArgs a{qkv, ld, nullptr, 0, nullptr, nullptr, nullptr, decay, state, cu, ctx, slots, out, H, N, P, 1};
+  return f32 ? scan_launch_t<float, 1>(a, B, s) : scan_launch_t<__nv_bfloat16, 1>(a, B, s);
+}
+
+cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L, int R, const float* qn_w, const float* kvn_w, float eps,
+                                   void* cq, void* pool, const int* slot_map, const int* positions, const float* inv_freq, bool f32, int T,
+                                   cudaStream_t s) {
+  AT_DISPATCH(f32, (latent_prologue_kernel<AT><<<T, 256, 0, s>>>((const AT*)x, ld_x, Qr, L, R, qn_w, kvn_w, eps, (AT*)cq, (AT*)pool, slot_map,
+                                                                 positions, inv_freq)));
+  return last();
+}
+
+cudaError_t latent_attention_launch(const void* q, const void* pool, const float* sink, const int* block_tables, int max_blocks,
+                                    const int* positions, const int* cu, int B, int H, int L, int R, int page, float scale,
+                                    const float* inv_freq, void* out, bool f32, int T, cudaStream_t s) {
+  if (L > 32 * kLatMaxPerLane) return cudaErrorInvalidValue;
+  const int nw = H < 8 ? H : 8, Dq = L + R;
+  const size_t smem = ((size_t)nw * Dq + (size_t)kLatTile * (Dq + 1)) * sizeof(float);
+  dim3 grid(T, (H + nw - 1) / nw);
+  if (f32) {
+    auto k = latent_attention_kernel<float>;
+    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+    k<<<grid, nw * 32, smem, s>>>((const float*)q, (const float*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R, page, scale,
+                                  inv_freq, (float*)out);
+  } else {
+    auto k = latent_attention_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+    k<<<grid, nw * 32, smem, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R,
+                                  page, scale, inv_freq, (__nv_bfloat16*)out);
+  }
+  return last();
+}
+
+}  // namespace b200
