@@ -1,0 +1,175 @@
+"""Perelorn beside the framework's closest existing model (DeepSeek-V2 with dense feed-forwards: latent attention, same width and
+about the same weight bytes), random weights, bf16, one GPU: prefill and decode throughput of the whole stack, and the time of each
+new kernel against the HBM roofline (``MEASURED_PEAKS.json``), with the like kernel of the closest model where there is one.
+
+    python bench.py --arch perelorn [--arch-sizes 1024,2048]        (prints one JSON line per measurement)
+
+Timing: CUDA events on the launching stream, 3 warm-up runs, an L2 flush (256 MiB write) before every timed run, median of 7.
+"""
+from __future__ import annotations
+
+import json
+import os
+import statistics
+import sys
+
+import torch
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+
+from mlx_sharding_b200.config import deepseek_v2_lite_config, perelorn_config  # noqa: E402
+from mlx_sharding_b200.ops.meta import BatchMeta  # noqa: E402
+from mlx_sharding_b200.parallel.pipeline import StageExecutor  # noqa: E402
+from mlx_sharding_b200.utils.loader import random_model  # noqa: E402
+from mlx_sharding_b200.utils.timing import flush_l2  # noqa: E402
+
+PS = 64
+
+
+def peaks():
+    try:
+        with open(os.path.join(os.path.dirname(os.path.dirname(os.path.abspath(__file__))), "MEASURED_PEAKS.json")) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "of measured"
+    except Exception:
+        return 6650.0, "of fallback"
+
+
+def timed(fn, warm=3, reps=7):
+    for _ in range(warm):
+        fn()
+    ts = []
+    for _ in range(reps):
+        flush_l2()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        a.record()
+        fn()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b))
+    return statistics.median(ts)
+
+
+def step_meta(B, q, ctx0, dev, slots=True):
+    pages_per = (ctx0 + q + PS - 1) // PS
+    bts = [list(range(1 + b * pages_per, 1 + (b + 1) * pages_per)) for b in range(B)]
+    return BatchMeta.build([q] * B, [ctx0] * B, bts, PS, device=dev, state_slots=list(range(1, B + 1)) if slots else None), 1 + B * pages_per
+
+
+def dense_deepseek(width, layers, vocab):
+    return deepseek_v2_lite_config(hidden_size=width, num_hidden_layers=layers, n_routed_experts=None, n_shared_experts=None,
+                                   intermediate_size=4 * width, vocab_size=vocab, first_k_dense_replace=layers, rope_scaling=None)
+
+
+def model_runs(name, model, B_dec, ctx_dec, S_pre, dev, hybrid):
+    out = {}
+    meta_p, pages_p = step_meta(1, S_pre, 0, dev, hybrid)
+    meta_d, pages_d = step_meta(B_dec, 1, ctx_dec - 1, dev, hybrid)
+    stage = StageExecutor(model, max(pages_p, pages_d) + 1, PS, num_state_slots=B_dec + 1)
+    tok_p = torch.randint(0, model.cfg.vocab_size, (S_pre,), device=dev)
+    tok_d = torch.randint(0, model.cfg.vocab_size, (B_dec,), device=dev)
+    ms = timed(lambda: stage.forward(tok_p, meta_p))
+    out["prefill_tok_s"] = S_pre / ms * 1e3
+    out["prefill_ms"] = ms
+    fwd = lambda: stage.forward(tok_d, meta_d)
+    ms_eager = timed(fwd)
+    graph = None
+    try:
+        torch.cuda.synchronize()
+        side = torch.cuda.Stream()
+        with torch.cuda.stream(side):
+            for _ in range(2):
+                fwd()
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            fwd()
+        ms = timed(graph.replay)
+        out["decode_mode"] = "cuda graph"
+    except Exception as e:  # noqa: BLE001
+        ms, out["decode_mode"] = ms_eager, f"eager (capture failed: {type(e).__name__})"
+    out["decode_tok_s"] = B_dec / ms * 1e3
+    out["decode_ms"] = ms
+    out["decode_eager_ms"] = ms_eager
+    out["weights_gb"] = model.weight_bytes() / 1e9
+    del graph
+    return out
+
+
+def kernel_table(width, dev, hbm):
+    """Each new kernel alone at one layer's shapes: decode (B=64 sequences, context 2048) is bound by the state / pool bytes it must
+    move; prefill (one 2048-token prompt) is reported as time and tokens/s."""
+    from mlx_sharding_b200.ops import b200 as O
+
+    rows = []
+    H, P, N, Hl, D, Lr, R = 2 * width // 64, 64, 128, 16, 128, 512, 64
+    bf = torch.bfloat16
+
+    def add(name, ms, nbytes, like=None):
+        r = dict(kernel=name, ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_hbm=round(nbytes / ms / 1e6 / hbm, 3))
+        if like:
+            r["like_kernel"] = like
+        rows.append(r)
+
+    for phase, B, q, ctx0 in (("decode", 64, 1, 2047), ("prefill", 1, 2048, 0)):
+        meta, _ = step_meta(B, q, ctx0, dev)
+        T = B * q
+        # selective scan
+        xbc = torch.randn(T, H * P + 2 * N, device=dev).to(bf)
+        dt = torch.randn(T, H, device=dev).to(bf)
+        st = torch.zeros(B + 1, H, N, P, device=dev)
+        v = [torch.randn(H, device=dev) for _ in range(3)]
+        ms = timed(lambda: O.ssm_scan(xbc, dt, v[0], v[1], v[2], st, meta, H, P, N, 1))
+        add(f"ssm_scan {phase}", ms, 2 * B * H * N * P * 4 + T * (H * P * 6 + 2 * N * 2))
+        cw, cb = torch.randn(xbc.shape[1], 4, device=dev), torch.randn(xbc.shape[1], device=dev)
+        cs = torch.zeros(B + 1, 3, xbc.shape[1], device=dev, dtype=bf)
+        ms = timed(lambda: O.causal_conv_silu(xbc, cw, cb, cs, meta))
+        add(f"causal_conv_silu {phase}", ms, T * xbc.shape[1] * 4 + 2 * B * 3 * xbc.shape[1] * 2)
+        # decayed linear attention
+        qkv = torch.randn(T, Hl * (3 * D + D), device=dev).to(bf)
+        st2 = torch.zeros(B + 1, Hl, D, D, device=dev)
+        dec = torch.full((Hl,), 0.97, device=dev)
+        ms = timed(lambda: O.decay_scan(qkv, dec, st2, meta, Hl, D, D))
+        add(f"decay_scan {phase}", ms, 2 * B * Hl * D * D * 4 + T * Hl * D * (3 * 2 + 4))
+        # latent attention with sink vs. the framework's absorbed-latent MLA decode kernel (same shapes: 16 heads, 512 + 64)
+        pool = torch.randn(1 + B * ((ctx0 + q + PS - 1) // PS), 1, PS, Lr + R, device=dev).to(bf)
+        qq = torch.randn(T, Hl, Lr + R, device=dev).to(bf)
+        sink = torch.zeros(Hl, device=dev)
+        inv = torch.rand(R // 2, device=dev)
+        nbytes = B * (ctx0 + q) * (Lr + R) * 2 + T * Hl * (2 * Lr + R) * 2
+        ms = timed(lambda: O.latent_attention(qq, pool, sink, meta, 0.07, Lr, inv))
+        add(f"latent_attention(sink) {phase}", ms, nbytes)
+        if phase == "decode":
+            ms = timed(lambda: O.mla_decode(qq, pool, meta, 0.07))
+            add("mla_decode (DeepSeek-V2 absorbed, tcgen05) decode", ms, nbytes, like="latent_attention(sink) decode")
+    return rows
+
+
+def main(sizes=(1024, 2048)):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, tag = peaks()
+    for width in sizes:
+        pc = perelorn_config(width=width, vocab=32000, blocks=2, heads=16, ff=4 * width, side_dim=64)
+        pm = random_model(pc, dtype=torch.bfloat16, device=dev, seed=1)
+        pbytes = pm.weight_bytes()
+        r = model_runs("perelorn", pm, 32, 1024, 2048, dev, True)
+        print(json.dumps(dict(bench="arch", model="perelorn", width=width, layers=len(pc["layers"]), **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})), flush=True)
+        del pm
+        torch.cuda.empty_cache()
+        # closest existing model at about equal weight bytes: pick its depth from the bytes of a 1- and a 2-layer build
+        b1 = random_model(dense_deepseek(width, 1, 32000), dtype=torch.bfloat16, device=dev, seed=1).weight_bytes()
+        b2 = random_model(dense_deepseek(width, 2, 32000), dtype=torch.bfloat16, device=dev, seed=1).weight_bytes()
+        layers = max(1, round((pbytes - (2 * b1 - b2)) / (b2 - b1)))
+        dm = random_model(dense_deepseek(width, layers, 32000), dtype=torch.bfloat16, device=dev, seed=1)
+        r = model_runs("deepseek_v2-dense", dm, 32, 1024, 2048, dev, False)
+        print(json.dumps(dict(bench="arch", model="deepseek_v2 (dense ff)", width=width, layers=layers, **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})), flush=True)
+        del dm
+        torch.cuda.empty_cache()
+    for row in kernel_table(sizes[-1], dev, hbm):
+        print(json.dumps(dict(bench="arch-kernel", roofline=f"{hbm} GB/s {tag}", **row)), flush=True)
+
+
+if __name__ == "__main__":
+    main(tuple(int(x) for x in sys.argv[1].split(",")) if len(sys.argv) > 1 else (1024, 2048))

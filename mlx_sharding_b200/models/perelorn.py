@@ -133,8 +133,8 @@ class PerelornStage(StageModel):
         return self
 
     # ---- forward ----------------------------------------------------------------------------------------------------
-    def _mm(self, x, W: LinearWeight, f32: bool = False):
-        y = self.ops.linear_any(x, W, torch.float32 if f32 else self.dtype)
+    def _mm(self, x, W: LinearWeight, f32: bool = False, act: str = "none"):
+        y = self.ops.linear_any(x, W, torch.float32 if f32 else self.dtype, act)
         return y if y.shape[1] == W.n_real else y[:, :W.n_real]
 
     def _mamba2(self, w, m, ha, meta, st):
@@ -179,7 +179,7 @@ class PerelornStage(StageModel):
             y = self._latent(i, w, m, ha, meta, kv.k[i])
         ha = O.post_norm_add_(h, y, w["norm1"], eps, self.dtype)
         if L["mlp"]:
-            y = self._mm(O.gelu_erf_(self._mm(ha, w["up"])), w["down"], True)
+            y = self._mm(self._mm(ha, w["up"], act="gelu_erf"), w["down"], True)      # exact gelu in the up-projection's epilogue
             ha = O.post_norm_add_(h, y, w["norm2"], eps, self.dtype)
         if c.token_side_dim:
             g = O.side_gate(self._mm(ha, w["side_gate"]), self.side_table, tokens, i * c.token_side_dim)

@@ -20,7 +20,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_b200_C.so")
 _C = None
 
-ACT_IDS = {"none": 0, "silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "gelu_approx": 2}
+ACT_IDS = {"none": 0, "silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "gelu_approx": 2, "gelu_erf": 3}
 
 
 def load_extension(build_if_missing: bool = False):
@@ -491,15 +491,20 @@ def _slots(meta: BatchMeta) -> torch.Tensor:
     return meta.state_slots
 
 
-def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype) -> torch.Tensor:
-    """``x @ W^T``.  bf16 operands whose shapes fit the TMA rules (K and N multiples of 8, 16-byte aligned rows) take the tcgen05 GEMM;
+def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
+    """``act(x @ W^T)``.  bf16 operands whose shapes fit the TMA rules (K and N multiples of 8, 16-byte aligned rows) take the tcgen05 GEMM;
     fp32 operands (exact mode) and odd shapes go to cuBLAS."""
     w = W.weight
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] > 0):
-        return C().linear(x, w, None, None, None, 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+        return C().linear(x, w, None, None, None, ACT_IDS[act], 0.0, out_dtype == torch.float32, None, 0, 0, 0)
     y = torch.nn.functional.linear(x, w)
-    return y if y.dtype == out_dtype else y.to(out_dtype)
+    y = y if y.dtype == out_dtype else y.to(out_dtype)
+    if act == "gelu_erf":
+        return gelu_erf_(y)
+    if act != "none":
+        raise NotImplementedError(act)
+    return y
 
 
 def gather_rows(table, ids, col0: int, ncols: int, out_dtype):
@@ -544,4 +549,5 @@ def latent_kv_prologue(dqkv, q_rank: int, kv_rank: int, qn_w, kvn_w, eps: float,
 
 
 def latent_attention(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None):
-    return C().hy_latent_attention(q, pool, sink, meta.block_tables, meta.positions, meta.cu_seqlens, float(scale), int(kv_rank), inv_freq)
+    return C().hy_latent_attention(q, pool, sink, meta.block_tables, meta.positions, meta.cu_seqlens, float(scale), int(kv_rank), inv_freq,
+                                   int(meta.max_ctx_len))

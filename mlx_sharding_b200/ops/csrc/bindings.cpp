@@ -117,6 +117,7 @@ Tensor linear(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& w2,
   if (bias.has_value()) { check_bf16(*bias, "bias"); a.bias = bias->data_ptr(); }
   a.act = (int)act; a.softcap = (float)softcap;
   int sp = splits > 0 ? (int)splits : auto_splits((int)T, (int)N, (int)K, false);
+  if (act != 0 && !w2.has_value()) sp = 1;   // activation epilogue of a single GEMM: applied to complete sums only
   a.splits = sp;
   auto& sc = scratch();
   Tensor ctr = sc.get_counters(x.device());
@@ -926,7 +927,7 @@ Tensor hy_latent_prologue(const Tensor& x, int64_t Qr, int64_t L, const Tensor& 
 }
 
 Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& sink, const Tensor& block_tables, const Tensor& positions,
-                           const Tensor& cu, double scale, int64_t L, const Tensor& inv_freq) {
+                           const Tensor& cu, double scale, int64_t L, const Tensor& inv_freq, int64_t max_ctx) {
   check_act(q, "q"); check_f32c(sink, "sink"); check_f32c(inv_freq, "inv_freq"); check_i32(block_tables, "block_tables");
   check_i32(positions, "positions"); check_i32(cu, "cu_seqlens");
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && pool.is_contiguous() && pool.dim() == 4 && pool.size(1) == 1 && pool.size(3) == q.size(2) &&
@@ -936,9 +937,22 @@ Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& si
   const c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty({T, H, L}, q.options());
   if (T == 0) return out;
+  // few query rows over long contexts (decode): split the keys over CTAs so the grid fills the GPU; partial (m, l, o) are merged
+  // with the sink by a second kernel
+  const int64_t ctas = T * ((H + 7) / 8);
+  int64_t nsplit = 1, chunk = 1 << 30;
+  if (ctas < 2 * sm_count() && max_ctx > 256) {
+    nsplit = std::min<int64_t>({(2 * sm_count() + ctas - 1) / ctas, (max_ctx + 127) / 128, (int64_t)32});
+    chunk = ((max_ctx + nsplit - 1) / nsplit + 31) / 32 * 32;
+    nsplit = (max_ctx + chunk - 1) / chunk;
+  }
+  Tensor part;
+  if (nsplit > 1) part = torch::empty({T * H * nsplit * (L + 2)}, q.options().dtype(torch::kFloat32));
+  else chunk = 1 << 30;
   LAUNCH_OK(b200::latent_attention_launch(q.data_ptr(), pool.data_ptr(), sink.data_ptr<float>(), block_tables.data_ptr<int>(), (int)block_tables.size(1),
                                           positions.data_ptr<int>(), cu.data_ptr<int>(), (int)(cu.numel() - 1), (int)H, (int)L, (int)R, (int)pool.size(2),
-                                          (float)scale, inv_freq.data_ptr<float>(), out.data_ptr(), is_f32(q), (int)T, cur_stream()));
+                                          (float)scale, inv_freq.data_ptr<float>(), out.data_ptr(), is_f32(q), (int)T, (int)nsplit, (int)chunk,
+                                          nsplit > 1 ? part.data_ptr<float>() : nullptr, cur_stream()));
   return out;
 }
 

@@ -199,57 +199,66 @@ struct ScanArgs {
   int H, N, P, G;
 };
 
+constexpr int kScanTokens = 16;   // tokens whose operands are staged in shared memory at a time
+
 template <typename AT, int MODE>
-__global__ void recurrent_scan_kernel(ScanArgs a) {
+__global__ void recurrent_scan_kernel(ScanArgs a, int PB) {
   extern __shared__ float smem[];
-  const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H;
-  const int R = blockDim.x / P, p = threadIdx.x % P, r = threadIdx.x / P;
-  float* S = smem;                         // [N][P]
-  float* red = smem + N * P;               // [2][R][P]
+  const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H, p0 = blockIdx.z * PB;
+  const int R = blockDim.x / PB, p = threadIdx.x % PB, r = threadIdx.x / PB;
+  float* S = smem;                          // [N][PB]   this CTA's columns p0 .. p0 + PB of the head's state
+  float* red = S + N * PB;                  // [2][R][PB]
+  float* kq = red + 2 * R * PB;             // [tokens][2N]  k (already scaled) | q
+  float* xs = kq + kScanTokens * 2 * N;     // [tokens][PB]
+  float* dc = xs + kScanTokens * PB;        // [tokens]      decay
   const int s = a.cu[b], q = a.cu[b + 1] - s;
   if (q == 0) return;
   const bool fresh = a.ctx[b] - q == 0;
   float* gs = a.state + ((long long)a.slots[b] * H + h) * N * P;
-  for (int i = threadIdx.x; i < N * P; i += blockDim.x) S[i] = fresh ? 0.f : gs[i];
-  __syncthreads();
+  for (int i = threadIdx.x; i < N * PB; i += blockDim.x) S[i] = fresh ? 0.f : gs[(i / PB) * P + p0 + i % PB];
   const AT* in = reinterpret_cast<const AT*>(a.in);
   const int g = MODE == 0 ? h / (H / a.G) : 0;
   const float Aneg = MODE == 0 ? -expf(a.A_log[h]) : 0.f, Dh = MODE == 0 ? a.D[h] : 0.f, dtb = MODE == 0 ? a.dt_bias[h] : 0.f;
   const float dec = MODE == 1 ? a.decay[h] : 0.f;
-  for (int j = 0; j < q; ++j) {
-    const AT* row = in + (long long)(s + j) * a.ld_in;
-    const AT *kp, *qp;
-    float decay, kscale, xv;
-    if (MODE == 0) {
-      const float dt = softplus_f(ldf<AT>(reinterpret_cast<const AT*>(a.dt) + (long long)(s + j) * a.ld_dt + h) + dtb);
-      decay = expf(Aneg * dt); kscale = dt;
-      xv = ldf<AT>(row + h * P + p);
-      kp = row + H * P + g * N; qp = row + H * P + a.G * N + g * N;
-    } else {
-      decay = dec; kscale = 1.f;
-      qp = row + h * N; kp = row + H * N + h * N;
-      xv = silu_f(ldf<AT>(row + 2 * H * N + h * P + p));
-    }
-    float acc = 0.f;
-    if (r < R) {
-      for (int n = r; n < N; n += R) {
-        float kv = ldf<AT>(kp + n), qv = ldf<AT>(qp + n);
-        if (MODE == 1) { kv = silu_f(kv); qv = silu_f(qv); }
-        const float sv = decay * S[n * P + p] + (kscale * kv) * xv;
-        S[n * P + p] = sv;
-        acc += sv * qv;
-      }
-      red[((j & 1) * R + r) * P + p] = acc;
+  for (int j0 = 0; j0 < q; j0 += kScanTokens) {
+    const int nt = min(kScanTokens, q - j0);
+    __syncthreads();                        // the last block's operands are no longer read (and S is loaded)
+    for (int i = threadIdx.x; i < nt * (2 * N + PB + 1); i += blockDim.x) {
+      const int jj = i / (2 * N + PB + 1), e = i % (2 * N + PB + 1);
+      const AT* row = in + (long long)(s + j0 + jj) * a.ld_in;
+      float dt = 1.f;
+      if (MODE == 0 && (e < N || e == 2 * N + PB))
+        dt = softplus_f(ldf<AT>(reinterpret_cast<const AT*>(a.dt) + (long long)(s + j0 + jj) * a.ld_dt + h) + dtb);
+      if (e < N) kq[jj * 2 * N + e] = MODE == 0 ? dt * ldf<AT>(row + H * P + g * N + e) : silu_f(ldf<AT>(row + H * N + h * N + e));
+      else if (e < 2 * N) kq[jj * 2 * N + e] = MODE == 0 ? ldf<AT>(row + H * P + a.G * N + g * N + e - N) : silu_f(ldf<AT>(row + h * N + e - N));
+      else if (e < 2 * N + PB) xs[jj * PB + e - 2 * N] = MODE == 0 ? ldf<AT>(row + h * P + p0 + e - 2 * N)
+                                                                   : silu_f(ldf<AT>(row + 2 * H * N + h * P + p0 + e - 2 * N));
+      else dc[jj] = MODE == 0 ? expf(Aneg * dt) : dec;
     }
     __syncthreads();
-    if (r == 0) {
-      float y = 0.f;
-      for (int i = 0; i < R; ++i) y += red[((j & 1) * R + i) * P + p];
-      a.out[(long long)(s + j) * H * P + h * P + p] = y + Dh * xv;
+    for (int jj = 0; jj < nt; ++jj) {
+      const int j = j0 + jj;
+      const float decay = dc[jj], xv = xs[jj * PB + p];
+      const float* kr = kq + jj * 2 * N;
+      if (r < R) {
+        float acc = 0.f;
+        for (int n = r; n < N; n += R) {
+          const float sv = decay * S[n * PB + p] + kr[n] * xv;
+          S[n * PB + p] = sv;
+          acc += sv * kr[N + n];
+        }
+        red[((j & 1) * R + r) * PB + p] = acc;
+      }
+      __syncthreads();
+      if (r == 0) {
+        float y = 0.f;
+        for (int i = 0; i < R; ++i) y += red[((j & 1) * R + i) * PB + p];
+        a.out[(long long)(s + j) * H * P + h * P + p0 + p] = y + Dh * xv;
+      }
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < N * P; i += blockDim.x) gs[i] = S[i];
+  for (int i = threadIdx.x; i < N * PB; i += blockDim.x) gs[(i / PB) * P + p0 + i % PB] = S[i];
 }
 
 // ---------------------------------------------------------------------------------------------------------- latent attention
@@ -290,7 +299,8 @@ template <typename AT>
 __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ pool, const float* __restrict__ sink,
                                         const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ positions,
                                         const int* __restrict__ cu, int B, int H, int L, int R, int page, float scale,
-                                        const float* __restrict__ inv_freq, AT* __restrict__ out) {
+                                        const float* __restrict__ inv_freq, AT* __restrict__ out, int nsplit, int chunk,
+                                        float* __restrict__ part) {
   extern __shared__ float smem[];
   const int Dq = L + R, ldk = Dq + 1, nw = blockDim.x >> 5;
   float* qs = smem;                       // [nw][Dq]
@@ -318,15 +328,17 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
     }
     qs[i] = v;
   }
-  float m = h < H ? sink[h] : 0.f, l = 1.f;   // the sink: one extra term exp(sink - m), no key, no value
+  // the sink: one extra term exp(sink - m) of the denominator, no key, no value (added by the combine kernel when keys are split)
+  float m = nsplit > 1 ? -INFINITY : (h < H ? sink[h] : 0.f), l = nsplit > 1 ? 0.f : 1.f;
   float o[kLatMaxPerLane];
 #pragma unroll
   for (int i = 0; i < kLatMaxPerLane; ++i) o[i] = 0.f;
   const int nper = (L + 31) / 32;
   const float* qh = qs + warp * Dq;
-  for (int j0 = 0; j0 <= pos; j0 += kLatTile) {
+  const int jend = min(pos + 1, (int)(blockIdx.z + 1) * chunk);
+  for (int j0 = blockIdx.z * chunk; j0 < jend; j0 += kLatTile) {
     __syncthreads();
-    const int nk = min(kLatTile, pos + 1 - j0);
+    const int nk = min(kLatTile, jend - j0);
     for (int i = threadIdx.x; i < nk * Dq; i += blockDim.x) {
       const int jj = i / Dq, d = i % Dq, j = j0 + jj;
       ks[jj * ldk + d] = ldf<AT>(pool + ((long long)bt[j / page] * page + j % page) * Dq + d);
@@ -341,7 +353,7 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
       sc = acc * scale;
     }
     const float mn = fmaxf(m, warp_max(sc));
-    const float corr = expf(m - mn), pj = lane < nk ? expf(sc - mn) : 0.f;
+    const float corr = m == -INFINITY ? 0.f : expf(m - mn), pj = lane < nk ? expf(sc - mn) : 0.f;
     l = l * corr + warp_sum(pj);
     m = mn;
 #pragma unroll
@@ -354,11 +366,35 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
         if (i < nper) { const int d = lane + 32 * i; if (d < L) o[i] += pv * kr[d]; }
     }
   }
-  if (h < H) {
+  if (h < H && nsplit == 1) {
     const float inv = 1.f / l;
 #pragma unroll
     for (int i = 0; i < kLatMaxPerLane; ++i)
       if (i < nper) { const int d = lane + 32 * i; if (d < L) stf<AT>(out + ((long long)t * H + h) * L + d, o[i] * inv); }
+  } else if (h < H) {
+    float* pp = part + (((long long)t * H + h) * nsplit + blockIdx.z) * (L + 2);
+    if (lane == 0) { pp[0] = m; pp[1] = l; }
+#pragma unroll
+    for (int i = 0; i < kLatMaxPerLane; ++i)
+      if (i < nper) { const int d = lane + 32 * i; if (d < L) pp[2 + d] = o[i]; }
+  }
+}
+
+// merge the key splits of one (token, head): out = sum_z o_z e^(m_z - M) / (e^(sink - M) + sum_z l_z e^(m_z - M))
+template <typename AT>
+__global__ void latent_combine_kernel(const float* __restrict__ part, const float* __restrict__ sink, int H, int L, int nsplit,
+                                      AT* __restrict__ out) {
+  const long long th = blockIdx.x;
+  const float* pp = part + th * nsplit * (L + 2);
+  const float sk = sink[th % H];
+  float M = sk;
+  for (int z = 0; z < nsplit; ++z) M = fmaxf(M, pp[z * (L + 2)]);
+  float den = expf(sk - M);
+  for (int z = 0; z < nsplit; ++z) { const float mz = pp[z * (L + 2)]; if (mz != -INFINITY) den += pp[z * (L + 2) + 1] * expf(mz - M); }
+  for (int d = threadIdx.x; d < L; d += blockDim.x) {
+    float acc = 0.f;
+    for (int z = 0; z < nsplit; ++z) { const float mz = pp[z * (L + 2)]; if (mz != -INFINITY) acc += pp[z * (L + 2) + 2 + d] * expf(mz - M); }
+    stf<AT>(out + th * L + d, acc / den);
   }
 }
 
@@ -428,17 +464,20 @@ template <typename AT, int MODE>
 static cudaError_t scan_launch_t(const ScanArgs& a, int B, cudaStream_t s) {
   const int P = a.P, N = a.N;
   if (P > 1024) return cudaErrorInvalidValue;
-  int R = 256 / P;
+  // columns of the state are independent: split a head's value dimension over CTAs (PB columns each) while the grid is small
+  int PB = P;
+  while (PB > 16 && PB % 2 == 0 && (long long)B * a.H * (P / PB) < 592) PB /= 2;
+  int R = 256 / PB;
   if (R < 1) R = 1;
   if (R > N) R = N;
-  int threads = (R * P + 31) / 32 * 32;         // the tail threads (r >= R) only help with the state copy
-  const size_t smem = ((size_t)N * P + 2 * (size_t)R * P) * sizeof(float);
+  const int threads = (R * PB + 31) / 32 * 32;   // tail threads (r >= R) only help with staging and the state copy
+  const size_t smem = ((size_t)N * PB + 2 * (size_t)R * PB + (size_t)kScanTokens * (2 * N + PB + 1)) * sizeof(float);
   auto k = recurrent_scan_kernel<AT, MODE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  k<<<dim3(B, a.H), threads, smem, s>>>(a);
+  k<<<dim3(B, a.H, P / PB), threads, smem, s>>>(a, PB);
   return last();
 }
 
@@ -465,21 +504,23 @@ cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L,
 
 cudaError_t latent_attention_launch(const void* q, const void* pool, const float* sink, const int* block_tables, int max_blocks,
                                     const int* positions, const int* cu, int B, int H, int L, int R, int page, float scale,
-                                    const float* inv_freq, void* out, bool f32, int T, cudaStream_t s) {
-  if (L > 32 * kLatMaxPerLane) return cudaErrorInvalidValue;
+                                    const float* inv_freq, void* out, bool f32, int T, int nsplit, int chunk, float* part, cudaStream_t s) {
+  if (L > 32 * kLatMaxPerLane || nsplit < 1 || (nsplit > 1 && part == nullptr)) return cudaErrorInvalidValue;
   const int nw = H < 8 ? H : 8, Dq = L + R;
   const size_t smem = ((size_t)nw * Dq + (size_t)kLatTile * (Dq + 1)) * sizeof(float);
-  dim3 grid(T, (H + nw - 1) / nw);
+  dim3 grid(T, (H + nw - 1) / nw, nsplit);
   if (f32) {
     auto k = latent_attention_kernel<float>;
     if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
     k<<<grid, nw * 32, smem, s>>>((const float*)q, (const float*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R, page, scale,
-                                  inv_freq, (float*)out);
+                                  inv_freq, (float*)out, nsplit, chunk, part);
+    if (nsplit > 1) latent_combine_kernel<float><<<T * H, 128, 0, s>>>(part, sink, H, L, nsplit, (float*)out);
   } else {
     auto k = latent_attention_kernel<__nv_bfloat16>;
     if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
     k<<<grid, nw * 32, smem, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R,
-                                  page, scale, inv_freq, (__nv_bfloat16*)out);
+                                  page, scale, inv_freq, (__nv_bfloat16*)out, nsplit, chunk, part);
+    if (nsplit > 1) latent_combine_kernel<__nv_bfloat16><<<T * H, 128, 0, s>>>(part, sink, H, L, nsplit, (__nv_bfloat16*)out);
   }
   return last();
 }

@@ -26,5 +26,5 @@ cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L,
                                    cudaStream_t s);
 cudaError_t latent_attention_launch(const void* q, const void* pool, const float* sink, const int* block_tables, int max_blocks,
                                     const int* positions, const int* cu, int B, int H, int L, int R, int page, float scale,
-                                    const float* inv_freq, void* out, bool f32, int T, cudaStream_t s);
+                                    const float* inv_freq, void* out, bool f32, int T, int nsplit, int chunk, float* part, cudaStream_t s);
 }  // namespace b200

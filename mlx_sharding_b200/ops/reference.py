@@ -477,6 +477,11 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: torch.Tensor, me
     return out.to(out_dtype)
 
 
-def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype) -> torch.Tensor:
-    """``x @ W^T`` for any shape / float dtype (fp32 accumulate)."""
-    return linear(x, W, out_dtype=out_dtype)
+def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: str = "none") -> torch.Tensor:
+    """``act(x @ W^T)`` for any shape / float dtype (fp32 accumulate; ``act``: none | gelu_erf)."""
+    y = linear(x, W, out_dtype=torch.float32)
+    if act == "gelu_erf":
+        y = F.gelu(y)
+    elif act != "none":
+        raise NotImplementedError(act)
+    return y.to(out_dtype)
