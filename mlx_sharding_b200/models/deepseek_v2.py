@@ -107,7 +107,7 @@ class DeepseekV2Stage(StageModel):
             m = _EXPERT_RE.match(k)
             if m:
                 groups.setdefault((m.group(1), m.group(3), m.group(4)), {})[int(m.group(2))] = sd.pop(k)
-        n = self.cfg.n_routed_experts
+        n = self.cfg.n_routed_experts or 0       # a config without routed experts is a dense model
         want = list(range(n))
         if self.expert_shard is not None:  # expert parallelism: only this rank's experts were read (utils/checkpoint.py)
             r, world = self.expert_shard
