@@ -38,6 +38,7 @@ def _pad_rows(w: torch.Tensor, mult: int = 8) -> torch.Tensor:
 
 class PerelornStage(StageModel):
     arch = "perelorn"
+    PREFILL_GEMM_MIN_ROWS = 32
 
     def __init__(self, cfg, spec=None, dtype=torch.bfloat16, device="cpu", backend=None):
         super().__init__(cfg, spec, dtype, device, backend)
@@ -164,7 +165,10 @@ class PerelornStage(StageModel):
         q = self._mm(cq, w["q_abs"])
         if not q.is_contiguous():
             q = q.contiguous()
-        o = O.latent_attention(q.view(T, H, Lr + R), pool, w["sink"], meta, float(m["scale"]), Lr, self.rope_freqs[i],
+        # one sequence with a long portion (prompt prefill): two tensor-core GEMMs around a masked softmax; ragged / decode steps: the
+        # paged multi-query kernel
+        attend = O.latent_attention_prefill if (meta.num_seqs == 1 and T >= self.PREFILL_GEMM_MIN_ROWS) else O.latent_attention
+        o = attend(q.view(T, H, Lr + R), pool, w["sink"], meta, float(m["scale"]), Lr, self.rope_freqs[i],
                                self.dtype)
         return self._mm(o.view(T, H * Lr), w["o"], True)
 

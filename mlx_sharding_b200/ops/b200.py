@@ -537,11 +537,11 @@ def causal_conv_silu(u, w, b, conv_state, meta: BatchMeta):
 
 def ssm_scan(xbc, dt_raw, dt_bias, A_log, D, state, meta: BatchMeta, heads: int, vdim: int, nstate: int, groups: int):
     return C().hy_ssm_scan(xbc, dt_raw, dt_bias, A_log, D, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(vdim),
-                           int(nstate), int(groups))
+                           int(nstate), int(groups), int(meta.max_q_len))
 
 
 def decay_scan(qkv, decay, state, meta: BatchMeta, heads: int, dim: int, vdim: int):
-    return C().hy_decay_scan(qkv, decay, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(dim), int(vdim))
+    return C().hy_decay_scan(qkv, decay, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(dim), int(vdim), int(meta.max_q_len))
 
 
 def latent_kv_prologue(dqkv, q_rank: int, kv_rank: int, qn_w, kvn_w, eps: float, pool, meta: BatchMeta, inv_freq):
@@ -551,3 +551,29 @@ def latent_kv_prologue(dqkv, q_rank: int, kv_rank: int, qn_w, kvn_w, eps: float,
 def latent_attention(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None):
     return C().hy_latent_attention(q, pool, sink, meta.block_tables, meta.positions, meta.cu_seqlens, float(scale), int(kv_rank), inv_freq,
                                    int(meta.max_ctx_len))
+
+
+def latent_attention_prefill(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None):
+    """:func:`latent_attention` for a step that holds ONE sequence with many query rows (a prompt or a portion of one), as matrix
+    products: gather the sequence's cached rows ``K`` ``[ctx, kv_rank + rot]`` from its pages, ``S = Q K^T`` (fp32 out), the
+    masked softmax with the sink (``hy_sink_softmax``), ``out = P K[:, :kv_rank]``.  The two products run on the tensor cores
+    (tcgen05 GEMM; cuBLAS fp32 in exact mode); query rows are processed in blocks so the score matrix stays below 256 MB."""
+    T, H, Dq = q.shape
+    ctx, page = int(meta.max_ctx_len), pool.shape[2]
+    ctx0, npad = ctx - T, (ctx + 7) // 8 * 8
+    pages = meta.block_tables[0, :(ctx + page - 1) // page].long()
+    ids = (pages[:, None] * page + torch.arange(page, device=q.device)).reshape(-1)[:ctx]
+    if npad > ctx:
+        ids = torch.cat([ids, ids[:1].expand(npad - ctx)])           # padding columns: any finite row (their probability is 0)
+    K = gather_rows(pool.view(-1, Dq), ids.contiguous(), 0, Dq, q.dtype)
+    Wk, Wc = LinearWeight(weight=K), LinearWeight(weight=K[:, :kv_rank].t().contiguous())
+    C().hy_rotate_half_(q, meta.positions, inv_freq, int(kv_rank))
+    is32 = _is32(q.dtype)
+    block = max(1, (1 << 26) // (npad * H))
+    outs = []
+    for t0 in range(0, T, block):
+        n = min(T, t0 + block) - t0
+        s = linear_any(q[t0:t0 + n].reshape(n * H, Dq), Wk, torch.float32)
+        p = C().hy_sink_softmax(s, sink, int(H), int(ctx0 + t0), float(scale), is32)
+        outs.append(linear_any(p, Wc, q.dtype).view(n, H, kv_rank))
+    return outs[0] if len(outs) == 1 else torch.cat(outs)

@@ -884,7 +884,7 @@ Tensor hy_causal_conv_silu(const Tensor& u, const Tensor& w, const Tensor& bias,
 }
 
 Tensor hy_ssm_scan(const Tensor& xbc, const Tensor& dt, const Tensor& dt_bias, const Tensor& A_log, const Tensor& D, Tensor state, const Tensor& cu,
-                   const Tensor& ctx, const Tensor& slots, int64_t H, int64_t P, int64_t N, int64_t G) {
+                   const Tensor& ctx, const Tensor& slots, int64_t H, int64_t P, int64_t N, int64_t G, int64_t max_q) {
   check_act(xbc, "xbc"); check_rows(xbc, "xbc"); check_rows(dt, "dt"); check_f32c(dt_bias, "dt_bias"); check_f32c(A_log, "A_log"); check_f32c(D, "D");
   check_f32c(state, "state"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens"); check_i32(slots, "state_slots");
   TORCH_CHECK(dt.scalar_type() == xbc.scalar_type() && xbc.size(1) == H * P + 2 * G * N && dt.size(1) == H && H % G == 0 && P <= 1024);
@@ -893,12 +893,12 @@ Tensor hy_ssm_scan(const Tensor& xbc, const Tensor& dt, const Tensor& dt_bias, c
   Tensor out = torch::empty({xbc.size(0), H * P}, xbc.options().dtype(torch::kFloat32));
   LAUNCH_OK(b200::ssm_scan_launch(xbc.data_ptr(), xbc.stride(0), dt.data_ptr(), dt.stride(0), dt_bias.data_ptr<float>(), A_log.data_ptr<float>(),
                                   D.data_ptr<float>(), state.data_ptr<float>(), cu.data_ptr<int>(), ctx.data_ptr<int>(), slots.data_ptr<int>(),
-                                  out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)N, (int)P, (int)G, is_f32(xbc), cur_stream()));
+                                  out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)N, (int)P, (int)G, is_f32(xbc), (int)max_q, cur_stream()));
   return out;
 }
 
 Tensor hy_decay_scan(const Tensor& qkv, const Tensor& decay, Tensor state, const Tensor& cu, const Tensor& ctx, const Tensor& slots, int64_t H,
-                     int64_t Dk, int64_t V) {
+                     int64_t Dk, int64_t V, int64_t max_q) {
   check_act(qkv, "qkv"); check_rows(qkv, "qkv"); check_f32c(decay, "decay"); check_f32c(state, "state");
   check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens"); check_i32(slots, "state_slots");
   TORCH_CHECK(qkv.size(1) >= 2 * H * Dk + H * V && decay.numel() == H && V <= 1024);
@@ -907,7 +907,7 @@ Tensor hy_decay_scan(const Tensor& qkv, const Tensor& decay, Tensor state, const
   Tensor out = torch::empty({qkv.size(0), H * V}, qkv.options().dtype(torch::kFloat32));
   LAUNCH_OK(b200::decay_scan_launch(qkv.data_ptr(), qkv.stride(0), decay.data_ptr<float>(), state.data_ptr<float>(), cu.data_ptr<int>(),
                                     ctx.data_ptr<int>(), slots.data_ptr<int>(), out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)Dk, (int)V,
-                                    is_f32(qkv), cur_stream()));
+                                    is_f32(qkv), (int)max_q, cur_stream()));
   return out;
 }
 
@@ -956,6 +956,27 @@ Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& si
   return out;
 }
 
+
+Tensor hy_rotate_half_(Tensor q, const Tensor& positions, const Tensor& inv_freq, int64_t L) {
+  check_act(q, "q"); check_i32(positions, "positions"); check_f32c(inv_freq, "inv_freq");
+  TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && (q.size(2) - L) == 2 * inv_freq.numel() && positions.numel() >= q.size(0));
+  const c10::cuda::CUDAGuard guard(q.device());
+  if (q.size(0) == 0) return q;
+  LAUNCH_OK(b200::rotate_half_launch(q.data_ptr(), positions.data_ptr<int>(), inv_freq.data_ptr<float>(), (int)q.size(1), (int)L, (int)(q.size(2) - L),
+                                     is_f32(q), (int)q.size(0), cur_stream()));
+  return q;
+}
+
+Tensor hy_sink_softmax(const Tensor& s, const Tensor& sink, int64_t H, int64_t ctx0, double scale, bool out_f32) {
+  check_f32c(s, "scores"); check_f32c(sink, "sink");
+  TORCH_CHECK(s.dim() == 2 && sink.numel() == H && s.size(0) % H == 0);
+  const c10::cuda::CUDAGuard guard(s.device());
+  Tensor out = torch::empty({s.size(0), s.size(1)}, s.options().dtype(act_type(out_f32)));
+  if (s.size(0) == 0) return out;
+  LAUNCH_OK(b200::sink_softmax_launch(s.data_ptr<float>(), sink.data_ptr<float>(), (int)H, (int)s.size(1), (int)ctx0, (float)scale, out.data_ptr(), out_f32,
+                                      (long long)s.size(0), cur_stream()));
+  return out;
+}
 
 PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mlx_sharding_b200 sm_100a kernels";
@@ -1040,6 +1061,8 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hy_decay_scan", &hy_decay_scan);
   m.def("hy_latent_prologue", &hy_latent_prologue);
   m.def("hy_latent_attention", &hy_latent_attention);
+  m.def("hy_rotate_half_", &hy_rotate_half_);
+  m.def("hy_sink_softmax", &hy_sink_softmax);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });
   m.def("sm_arch", []() { return std::string("sm_100a"); });
 }

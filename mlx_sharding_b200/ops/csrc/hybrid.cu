@@ -25,6 +25,17 @@ template <typename T> __device__ __forceinline__ float rnd(float v);
 template <> __device__ __forceinline__ float rnd<float>(float v) { return v; }
 template <> __device__ __forceinline__ float rnd<__nv_bfloat16>(float v) { return __bfloat162float(__float2bfloat16_rn(v)); }
 
+// 16 bytes of activations -> floats
+template <typename T> __device__ __forceinline__ void unpack16(const uint4& v, float* dst);
+template <> __device__ __forceinline__ void unpack16<float>(const uint4& v, float* dst) {
+  dst[0] = __uint_as_float(v.x); dst[1] = __uint_as_float(v.y); dst[2] = __uint_as_float(v.z); dst[3] = __uint_as_float(v.w);
+}
+template <> __device__ __forceinline__ void unpack16<__nv_bfloat16>(const uint4& v, float* dst) {
+  const unsigned w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+  for (int i = 0; i < 4; ++i) { dst[2 * i] = __uint_as_float(w[i] << 16); dst[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u); }
+}
+
 __device__ __forceinline__ float silu_f(float v) { return v / (1.f + expf(-v)); }
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.f / (1.f + expf(-v)); }
 __device__ __forceinline__ float softplus_f(float v) { return v > 30.f ? v : log1pf(expf(v)); }
@@ -199,10 +210,10 @@ struct ScanArgs {
   int H, N, P, G;
 };
 
-constexpr int kScanTokens = 16;   // tokens whose operands are staged in shared memory at a time
+constexpr int kScanTokensMax = 16;   // tokens whose operands are staged in shared memory at a time (fewer for decode steps)
 
 template <typename AT, int MODE>
-__global__ void recurrent_scan_kernel(ScanArgs a, int PB) {
+__global__ void recurrent_scan_kernel(ScanArgs a, int PB, int kScanTokens) {
   extern __shared__ float smem[];
   const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H, p0 = blockIdx.z * PB;
   const int R = blockDim.x / PB, p = threadIdx.x % PB, r = threadIdx.x / PB;
@@ -215,7 +226,9 @@ __global__ void recurrent_scan_kernel(ScanArgs a, int PB) {
   if (q == 0) return;
   const bool fresh = a.ctx[b] - q == 0;
   float* gs = a.state + ((long long)a.slots[b] * H + h) * N * P;
-  for (int i = threadIdx.x; i < N * PB; i += blockDim.x) S[i] = fresh ? 0.f : gs[(i / PB) * P + p0 + i % PB];
+  const int rows_pass = blockDim.x / PB;     // rows of the state block copied per pass (thread (r, p) copies column p)
+  if (r < rows_pass)
+    for (int n = r; n < N; n += rows_pass) S[n * PB + p] = fresh ? 0.f : gs[n * P + p0 + p];
   const AT* in = reinterpret_cast<const AT*>(a.in);
   const int g = MODE == 0 ? h / (H / a.G) : 0;
   const float Aneg = MODE == 0 ? -expf(a.A_log[h]) : 0.f, Dh = MODE == 0 ? a.D[h] : 0.f, dtb = MODE == 0 ? a.dt_bias[h] : 0.f;
@@ -258,7 +271,8 @@ __global__ void recurrent_scan_kernel(ScanArgs a, int PB) {
     }
   }
   __syncthreads();
-  for (int i = threadIdx.x; i < N * PB; i += blockDim.x) gs[(i / PB) * P + p0 + i % PB] = S[i];
+  if (r < rows_pass)
+    for (int n = r; n < N; n += rows_pass) gs[n * P + p0 + p] = S[n * PB + p];
 }
 
 // ---------------------------------------------------------------------------------------------------------- latent attention
@@ -339,9 +353,20 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
   for (int j0 = blockIdx.z * chunk; j0 < jend; j0 += kLatTile) {
     __syncthreads();
     const int nk = min(kLatTile, jend - j0);
-    for (int i = threadIdx.x; i < nk * Dq; i += blockDim.x) {
-      const int jj = i / Dq, d = i % Dq, j = j0 + jj;
-      ks[jj * ldk + d] = ldf<AT>(pool + ((long long)bt[j / page] * page + j % page) * Dq + d);
+    // each warp fetches whole rows: 16-byte chunks per lane (several independent loads in flight), one block-table lookup per row
+    for (int jj = warp; jj < nk; jj += nw) {
+      const int j = j0 + jj;
+      const AT* src = pool + ((long long)bt[j / page] * page + j % page) * Dq;
+      float* dst = ks + jj * ldk;
+      constexpr int E = 16 / (int)sizeof(AT);
+      if (Dq % E == 0) {
+        for (int c = lane; c < Dq / E; c += 32) {
+          const uint4 v = *reinterpret_cast<const uint4*>(src + c * E);
+          unpack16<AT>(v, dst + c * E);
+        }
+      } else {
+        for (int d = lane; d < Dq; d += 32) dst[d] = ldf<AT>(src + d);
+      }
     }
     __syncthreads();
     if (h >= H) continue;
@@ -396,6 +421,47 @@ __global__ void latent_combine_kernel(const float* __restrict__ part, const floa
     for (int z = 0; z < nsplit; ++z) { const float mz = pp[z * (L + 2)]; if (mz != -INFINITY) acc += pp[z * (L + 2) + 2 + d] * expf(mz - M); }
     stf<AT>(out + th * L + d, acc / den);
   }
+}
+
+
+// ---- prefill of one sequence as two GEMMs: scores = Q K^T and out = P C (library / tcgen05 GEMMs) around these two kernels
+// rotate-half rotary, in place, on dims [L, L + R) of every head of q [T, H, L + R]
+template <typename AT>
+__global__ void rotate_half_kernel(AT* __restrict__ q, const int* __restrict__ positions, const float* __restrict__ inv_freq, int H, int L,
+                                   int R) {
+  const int t = blockIdx.x, half = R / 2;
+  const float pos = (float)positions[t];
+  for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
+    const int h = i / half, f = i % half;
+    AT* p = q + ((long long)t * H + h) * (L + R) + L;
+    float sn, cs;
+    sincosf(pos * inv_freq[f], &sn, &cs);
+    const float u = ldf<AT>(p + f), v = ldf<AT>(p + half + f);
+    stf<AT>(p + f, u * cs - v * sn);
+    stf<AT>(p + half + f, v * cs + u * sn);
+  }
+}
+
+// row r = (token t, head h) of raw scores [rows, n]; keys j <= ctx0 + t are visible; p_j = e^(s_j scale - m) / (e^(sink_h - m) + sum)
+template <typename AT>
+__global__ void sink_softmax_kernel(const float* __restrict__ s, const float* __restrict__ sink, int H, int n, int ctx0, float scale,
+                                    AT* __restrict__ out) {
+  __shared__ float red[32];
+  const long long r = blockIdx.x;
+  const int t = (int)(r / H), h = (int)(r % H), nv = min(n, ctx0 + t + 1);
+  const float* row = s + r * n;
+  const float sk = sink[h];
+  float m = sk;
+  for (int j = threadIdx.x; j < nv; j += blockDim.x) m = fmaxf(m, row[j] * scale);
+  m = warp_max(m);
+  const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
+  if (l == 0) red[w] = m;
+  __syncthreads();
+  m = warp_max(l < nw ? red[l] : -INFINITY);
+  float sum = 0.f;
+  for (int j = threadIdx.x; j < nv; j += blockDim.x) sum += expf(row[j] * scale - m);
+  const float inv = 1.f / (block_sum(sum, red) + expf(sk - m));
+  for (int j = threadIdx.x; j < n; j += blockDim.x) stf<AT>(out + r * n + j, j < nv ? expf(row[j] * scale - m) * inv : 0.f);
 }
 
 inline cudaError_t last() { return cudaGetLastError(); }
@@ -461,7 +527,7 @@ cudaError_t causal_conv_silu_launch(const void* u, long long ld_u, const float* 
 }
 
 template <typename AT, int MODE>
-static cudaError_t scan_launch_t(const ScanArgs& a, int B, cudaStream_t s) {
+static cudaError_t scan_launch_t(const ScanArgs& a, int B, int max_q, cudaStream_t s) {
   const int P = a.P, N = a.N;
   if (P > 1024) return cudaErrorInvalidValue;
   // columns of the state are independent: split a head's value dimension over CTAs (PB columns each) while the grid is small
@@ -471,27 +537,28 @@ static cudaError_t scan_launch_t(const ScanArgs& a, int B, cudaStream_t s) {
   if (R < 1) R = 1;
   if (R > N) R = N;
   const int threads = (R * PB + 31) / 32 * 32;   // tail threads (r >= R) only help with staging and the state copy
-  const size_t smem = ((size_t)N * PB + 2 * (size_t)R * PB + (size_t)kScanTokens * (2 * N + PB + 1)) * sizeof(float);
+  const int stage = max_q < 1 ? 1 : (max_q < kScanTokensMax ? max_q : kScanTokensMax);
+  const size_t smem = ((size_t)N * PB + 2 * (size_t)R * PB + (size_t)stage * (2 * N + PB + 1)) * sizeof(float);
   auto k = recurrent_scan_kernel<AT, MODE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return e;
   }
-  k<<<dim3(B, a.H, P / PB), threads, smem, s>>>(a, PB);
+  k<<<dim3(B, a.H, P / PB), threads, smem, s>>>(a, PB, stage);
   return last();
 }
 
 cudaError_t ssm_scan_launch(const void* xbc, long long ld_x, const void* dt, long long ld_dt, const float* dt_bias, const float* A_log,
                             const float* D, float* state, const int* cu, const int* ctx, const int* slots, float* out, int B, int H, int N,
-                            int P, int G, bool f32, cudaStream_t s) {
+                            int P, int G, bool f32, int max_q, cudaStream_t s) {
   ScanArgs a{xbc, ld_x, dt, ld_dt, dt_bias, A_log, D, nullptr, state, cu, ctx, slots, out, H, N, P, G};
-  return f32 ? scan_launch_t<float, 0>(a, B, s) : scan_launch_t<__nv_bfloat16, 0>(a, B, s);
+  return f32 ? scan_launch_t<float, 0>(a, B, max_q, s) : scan_launch_t<__nv_bfloat16, 0>(a, B, max_q, s);
 }
 
 cudaError_t decay_scan_launch(const void* qkv, long long ld, const float* decay, float* state, const int* cu, const int* ctx,
-                              const int* slots, float* out, int B, int H, int N, int P, bool f32, cudaStream_t s) {
+                              const int* slots, float* out, int B, int H, int N, int P, bool f32, int max_q, cudaStream_t s) {
   ScanArgs a{qkv, ld, nullptr, 0, nullptr, nullptr, nullptr, decay, state, cu, ctx, slots, out, H, N, P, 1};
-  return f32 ? scan_launch_t<float, 1>(a, B, s) : scan_launch_t<__nv_bfloat16, 1>(a, B, s);
+  return f32 ? scan_launch_t<float, 1>(a, B, max_q, s) : scan_launch_t<__nv_bfloat16, 1>(a, B, max_q, s);
 }
 
 cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L, int R, const float* qn_w, const float* kvn_w, float eps,
@@ -499,6 +566,17 @@ cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L,
                                    cudaStream_t s) {
   AT_DISPATCH(f32, (latent_prologue_kernel<AT><<<T, 256, 0, s>>>((const AT*)x, ld_x, Qr, L, R, qn_w, kvn_w, eps, (AT*)cq, (AT*)pool, slot_map,
                                                                  positions, inv_freq)));
+  return last();
+}
+
+cudaError_t rotate_half_launch(void* q, const int* positions, const float* inv_freq, int H, int L, int R, bool f32, int T, cudaStream_t s) {
+  AT_DISPATCH(f32, (rotate_half_kernel<AT><<<T, 128, 0, s>>>((AT*)q, positions, inv_freq, H, L, R)));
+  return last();
+}
+
+cudaError_t sink_softmax_launch(const float* sc, const float* sink, int H, int n, int ctx0, float scale, void* out, bool f32, long long rows,
+                                cudaStream_t s) {
+  AT_DISPATCH(f32, (sink_softmax_kernel<AT><<<(unsigned)rows, 256, 0, s>>>(sc, sink, H, n, ctx0, scale, (AT*)out)));
   return last();
 }
 

@@ -18,13 +18,16 @@ cudaError_t causal_conv_silu_launch(const void* u, long long ld_u, const float* 
                                     const int* ctx, const int* slots, int B, int C, int K, void* out, bool f32, int T, cudaStream_t s);
 cudaError_t ssm_scan_launch(const void* xbc, long long ld_x, const void* dt, long long ld_dt, const float* dt_bias, const float* A_log,
                             const float* D, float* state, const int* cu, const int* ctx, const int* slots, float* out, int B, int H, int N,
-                            int P, int G, bool f32, cudaStream_t s);
+                            int P, int G, bool f32, int max_q, cudaStream_t s);
 cudaError_t decay_scan_launch(const void* qkv, long long ld, const float* decay, float* state, const int* cu, const int* ctx,
-                              const int* slots, float* out, int B, int H, int N, int P, bool f32, cudaStream_t s);
+                              const int* slots, float* out, int B, int H, int N, int P, bool f32, int max_q, cudaStream_t s);
 cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L, int R, const float* qn_w, const float* kvn_w, float eps,
                                    void* cq, void* pool, const int* slot_map, const int* positions, const float* inv_freq, bool f32, int T,
                                    cudaStream_t s);
 cudaError_t latent_attention_launch(const void* q, const void* pool, const float* sink, const int* block_tables, int max_blocks,
                                     const int* positions, const int* cu, int B, int H, int L, int R, int page, float scale,
                                     const float* inv_freq, void* out, bool f32, int T, int nsplit, int chunk, float* part, cudaStream_t s);
+cudaError_t rotate_half_launch(void* q, const int* positions, const float* inv_freq, int H, int L, int R, bool f32, int T, cudaStream_t s);
+cudaError_t sink_softmax_launch(const float* sc, const float* sink, int H, int n, int ctx0, float scale, void* out, bool f32, long long rows,
+                                cudaStream_t s);
 }  // namespace b200

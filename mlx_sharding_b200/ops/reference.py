@@ -485,3 +485,8 @@ def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: st
     elif act != "none":
         raise NotImplementedError(act)
     return y.to(out_dtype)
+
+
+def latent_attention_prefill(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=torch.float32):
+    """Single-sequence prefill form of :func:`latent_attention` (the CUDA backend runs it as two GEMMs); same math here."""
+    return latent_attention(q, pool, sink, meta, scale, kv_rank, inv_freq, out_dtype)
