@@ -20,7 +20,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 _SO = os.path.join(_HERE, "_b200_C.so")
 _C = None
 
-ACT_IDS = {"none": 0, "silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "gelu_approx": 2, "gelu_erf": 3}
+ACT_IDS = {"none": 0, "silu": 1, "gelu_tanh": 2, "gelu_pytorch_tanh": 2, "gelu_approx": 2}
 
 
 def load_extension(build_if_missing: bool = False):
@@ -497,9 +497,10 @@ def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: st
     w = W.weight
     if (x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.shape[1] % 8 == 0 and w.shape[0] % 8 == 0 and x.stride(1) == 1
             and x.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and x.shape[0] > 0):
-        return C().linear(x, w, None, None, None, ACT_IDS[act], 0.0, out_dtype == torch.float32, None, 0, 0, 0)
-    y = torch.nn.functional.linear(x, w)
-    y = y if y.dtype == out_dtype else y.to(out_dtype)
+        y = C().linear(x, w, None, None, None, 0, 0.0, out_dtype == torch.float32, None, 0, 0, 0)
+    else:
+        y = torch.nn.functional.linear(x, w)
+        y = y if y.dtype == out_dtype else y.to(out_dtype)
     if act == "gelu_erf":
         return gelu_erf_(y)
     if act != "none":

@@ -117,7 +117,6 @@ Tensor linear(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& w2,
   if (bias.has_value()) { check_bf16(*bias, "bias"); a.bias = bias->data_ptr(); }
   a.act = (int)act; a.softcap = (float)softcap;
   int sp = splits > 0 ? (int)splits : auto_splits((int)T, (int)N, (int)K, false);
-  if (act != 0 && !w2.has_value()) sp = 1;   // activation epilogue of a single GEMM: applied to complete sums only
   a.splits = sp;
   auto& sc = scratch();
   Tensor ctr = sc.get_counters(x.device());

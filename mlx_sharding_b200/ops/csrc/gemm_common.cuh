@@ -40,7 +40,6 @@ __device__ __forceinline__ float apply_act(int act, float g) {
     float t = 1.0f - 2.0f / (1.0f + __expf(2.0f * u));  // tanh(u)
     return 0.5f * g * (1.0f + t);
   }
-  if (act == kActGeluErf) return 0.5f * g * (1.0f + erff(g * 0.7071067811865476f));
   return g;
 }
 
@@ -151,7 +150,6 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, uint8_t* smem,
         for (int j = 0; j < 16; ++j) {
           float y = g[j] + bias;
           if (DUAL) y = apply_act(p.act, y) * u[j];
-          else if (p.act != kActNone) y = apply_act(p.act, y);   // single GEMM with an activation epilogue (never split-K)
           if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
           stage_store<OutT>(&stg[(c + j) * kTileM + f_local], y);
         }

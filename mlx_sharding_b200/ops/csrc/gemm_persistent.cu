@@ -284,7 +284,6 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
           for (int j = 0; j < 16; ++j) {
             float y = g[j] + bias;
             if (DUAL) y = apply_act(p.act, y) * u[j];
-            else if (p.act != kActNone) y = apply_act(p.act, y);
             if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
             stage_store<OutT>(&stg[(c - c0 + j) * kTileM + f_local], y);
           }

@@ -7,7 +7,7 @@
 
 namespace b200 {
 
-enum : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2, kActGeluErf = 3 };
+enum : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
 
 // Device-side parameter block (passed by value).
 struct GemmParams {

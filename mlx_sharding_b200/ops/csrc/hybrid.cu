@@ -222,6 +222,7 @@ __global__ void recurrent_scan_kernel(ScanArgs a, int PB, int kScanTokens) {
   float* kq = red + 2 * R * PB;             // [tokens][2N]  k (already scaled) | q
   float* xs = kq + kScanTokens * 2 * N;     // [tokens][PB]
   float* dc = xs + kScanTokens * PB;        // [tokens]      decay
+  float* dts = dc + kScanTokens;            // [tokens]      step size
   const int s = a.cu[b], q = a.cu[b + 1] - s;
   if (q == 0) return;
   const bool fresh = a.ctx[b] - q == 0;
@@ -236,22 +237,33 @@ __global__ void recurrent_scan_kernel(ScanArgs a, int PB, int kScanTokens) {
   for (int j0 = 0; j0 < q; j0 += kScanTokens) {
     const int nt = min(kScanTokens, q - j0);
     __syncthreads();                        // the last block's operands are no longer read (and S is loaded)
-    for (int i = threadIdx.x; i < nt * (2 * N + PB + 1); i += blockDim.x) {
-      const int jj = i / (2 * N + PB + 1), e = i % (2 * N + PB + 1);
-      const AT* row = in + (long long)(s + j0 + jj) * a.ld_in;
-      float dt = 1.f;
-      if (MODE == 0 && (e < N || e == 2 * N + PB))
-        dt = softplus_f(ldf<AT>(reinterpret_cast<const AT*>(a.dt) + (long long)(s + j0 + jj) * a.ld_dt + h) + dtb);
-      if (e < N) kq[jj * 2 * N + e] = MODE == 0 ? dt * ldf<AT>(row + H * P + g * N + e) : silu_f(ldf<AT>(row + H * N + h * N + e));
-      else if (e < 2 * N) kq[jj * 2 * N + e] = MODE == 0 ? ldf<AT>(row + H * P + a.G * N + g * N + e - N) : silu_f(ldf<AT>(row + h * N + e - N));
-      else if (e < 2 * N + PB) xs[jj * PB + e - 2 * N] = MODE == 0 ? ldf<AT>(row + h * P + p0 + e - 2 * N)
-                                                                   : silu_f(ldf<AT>(row + 2 * H * N + h * P + p0 + e - 2 * N));
-      else dc[jj] = MODE == 0 ? expf(Aneg * dt) : dec;
+    if (MODE == 0) {                        // per-token step size and decay, once
+      for (int jj = threadIdx.x; jj < nt; jj += blockDim.x) {
+        const float dt = softplus_f(ldf<AT>(reinterpret_cast<const AT*>(a.dt) + (long long)(s + j0 + jj) * a.ld_dt + h) + dtb);
+        dts[jj] = dt;
+        dc[jj] = expf(Aneg * dt);
+      }
+      __syncthreads();
+    }
+    for (int e = threadIdx.x; e < 2 * N + PB; e += blockDim.x) {
+      // each thread owns operand columns e: its source column in the input row is fixed, the loads of the staged tokens are independent
+      int col;
+      if (MODE == 0) col = e < N ? H * P + g * N + e : (e < 2 * N ? H * P + a.G * N + g * N + (e - N) : h * P + p0 + (e - 2 * N));
+      else col = e < N ? H * N + h * N + e : (e < 2 * N ? h * N + (e - N) : 2 * H * N + h * P + p0 + (e - 2 * N));
+      const AT* src = in + (long long)(s + j0) * a.ld_in + col;
+#pragma unroll 4
+      for (int jj = 0; jj < nt; ++jj) {
+        float v = ldf<AT>(src + (long long)jj * a.ld_in);
+        if (MODE == 1) v = silu_f(v);
+        else if (e < N) v *= dts[jj];
+        if (e < 2 * N) kq[jj * 2 * N + e] = v;
+        else xs[jj * PB + e - 2 * N] = v;
+      }
     }
     __syncthreads();
     for (int jj = 0; jj < nt; ++jj) {
       const int j = j0 + jj;
-      const float decay = dc[jj], xv = xs[jj * PB + p];
+      const float decay = MODE == 0 ? dc[jj] : dec, xv = xs[jj * PB + p];
       const float* kr = kq + jj * 2 * N;
       if (r < R) {
         float acc = 0.f;
@@ -309,14 +321,16 @@ __global__ void latent_prologue_kernel(const AT* __restrict__ x, long long ld_x,
 constexpr int kLatTile = 32;
 constexpr int kLatMaxPerLane = 16;   // latent width <= 512
 
-template <typename AT>
+// VEC (kv_rank a multiple of 128, row width a multiple of 4): 16-byte shared-memory loads in both phases — lane l owns output dims
+// 4l + 128i .. +3 — and key rows padded to a multiple of 4 floats; otherwise scalar loads, lane l owns dims l + 32i, rows padded by 1.
+template <typename AT, bool VEC>
 __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ pool, const float* __restrict__ sink,
                                         const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ positions,
                                         const int* __restrict__ cu, int B, int H, int L, int R, int page, float scale,
                                         const float* __restrict__ inv_freq, AT* __restrict__ out, int nsplit, int chunk,
                                         float* __restrict__ part) {
   extern __shared__ float smem[];
-  const int Dq = L + R, ldk = Dq + 1, nw = blockDim.x >> 5;
+  const int Dq = L + R, ldk = VEC ? Dq + 4 : Dq + 1, nw = blockDim.x >> 5;
   float* qs = smem;                       // [nw][Dq]
   float* ks = smem + nw * Dq;             // [tile][Dq + 1]
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -362,7 +376,14 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
       if (Dq % E == 0) {
         for (int c = lane; c < Dq / E; c += 32) {
           const uint4 v = *reinterpret_cast<const uint4*>(src + c * E);
-          unpack16<AT>(v, dst + c * E);
+          if (VEC) {
+            float f[E];
+            unpack16<AT>(v, f);
+#pragma unroll
+            for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(dst + c * E + e) = make_float4(f[e], f[e + 1], f[e + 2], f[e + 3]);
+          } else {
+            unpack16<AT>(v, dst + c * E);
+          }
         }
       } else {
         for (int d = lane; d < Dq; d += 32) dst[d] = ldf<AT>(src + d);
@@ -374,7 +395,16 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
     if (lane < nk) {
       const float* kr = ks + lane * ldk;
       float acc = 0.f;
-      for (int d = 0; d < Dq; ++d) acc += qh[d] * kr[d];
+      if (VEC) {
+        const float4* q4 = reinterpret_cast<const float4*>(qh);
+        const float4* k4 = reinterpret_cast<const float4*>(kr);
+        for (int d = 0; d < Dq / 4; ++d) {
+          const float4 a = q4[d], b = k4[d];
+          acc += a.x * b.x + a.y * b.y + a.z * b.z + a.w * b.w;
+        }
+      } else {
+        for (int d = 0; d < Dq; ++d) acc += qh[d] * kr[d];
+      }
       sc = acc * scale;
     }
     const float mn = fmaxf(m, warp_max(sc));
@@ -386,22 +416,36 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
     for (int jj = 0; jj < nk; ++jj) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const float* kr = ks + jj * ldk;
+      if (VEC) {
 #pragma unroll
-      for (int i = 0; i < kLatMaxPerLane; ++i)
-        if (i < nper) { const int d = lane + 32 * i; if (d < L) o[i] += pv * kr[d]; }
+        for (int i = 0; i < kLatMaxPerLane / 4; ++i)
+          if (i < L / 128) {
+            const float4 c = *reinterpret_cast<const float4*>(kr + 4 * lane + 128 * i);
+            o[4 * i] += pv * c.x; o[4 * i + 1] += pv * c.y; o[4 * i + 2] += pv * c.z; o[4 * i + 3] += pv * c.w;
+          }
+      } else {
+#pragma unroll
+        for (int i = 0; i < kLatMaxPerLane; ++i)
+          if (i < nper) { const int d = lane + 32 * i; if (d < L) o[i] += pv * kr[d]; }
+      }
     }
   }
+  // register i of a lane holds output dim: VEC 4 lane + 128 (i / 4) + i % 4, else lane + 32 i
   if (h < H && nsplit == 1) {
     const float inv = 1.f / l;
 #pragma unroll
-    for (int i = 0; i < kLatMaxPerLane; ++i)
-      if (i < nper) { const int d = lane + 32 * i; if (d < L) stf<AT>(out + ((long long)t * H + h) * L + d, o[i] * inv); }
+    for (int i = 0; i < kLatMaxPerLane; ++i) {
+      const int d = VEC ? 4 * lane + 128 * (i / 4) + (i % 4) : lane + 32 * i;
+      if (d < L) stf<AT>(out + ((long long)t * H + h) * L + d, o[i] * inv);
+    }
   } else if (h < H) {
     float* pp = part + (((long long)t * H + h) * nsplit + blockIdx.z) * (L + 2);
     if (lane == 0) { pp[0] = m; pp[1] = l; }
 #pragma unroll
-    for (int i = 0; i < kLatMaxPerLane; ++i)
-      if (i < nper) { const int d = lane + 32 * i; if (d < L) pp[2 + d] = o[i]; }
+    for (int i = 0; i < kLatMaxPerLane; ++i) {
+      const int d = VEC ? 4 * lane + 128 * (i / 4) + (i % 4) : lane + 32 * i;
+      if (d < L) pp[2 + d] = o[i];
+    }
   }
 }
 
@@ -538,7 +582,7 @@ static cudaError_t scan_launch_t(const ScanArgs& a, int B, int max_q, cudaStream
   if (R > N) R = N;
   const int threads = (R * PB + 31) / 32 * 32;   // tail threads (r >= R) only help with staging and the state copy
   const int stage = max_q < 1 ? 1 : (max_q < kScanTokensMax ? max_q : kScanTokensMax);
-  const size_t smem = ((size_t)N * PB + 2 * (size_t)R * PB + (size_t)stage * (2 * N + PB + 1)) * sizeof(float);
+  const size_t smem = ((size_t)N * PB + 2 * (size_t)R * PB + (size_t)stage * (2 * N + PB + 2)) * sizeof(float);
   auto k = recurrent_scan_kernel<AT, MODE>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -585,21 +629,23 @@ cudaError_t latent_attention_launch(const void* q, const void* pool, const float
                                     const float* inv_freq, void* out, bool f32, int T, int nsplit, int chunk, float* part, cudaStream_t s) {
   if (L > 32 * kLatMaxPerLane || nsplit < 1 || (nsplit > 1 && part == nullptr)) return cudaErrorInvalidValue;
   const int nw = H < 8 ? H : 8, Dq = L + R;
-  const size_t smem = ((size_t)nw * Dq + (size_t)kLatTile * (Dq + 1)) * sizeof(float);
+  const bool vec = L % 128 == 0 && Dq % 4 == 0;
+  const size_t smem = ((size_t)nw * Dq + (size_t)kLatTile * (Dq + (vec ? 4 : 1))) * sizeof(float);
   dim3 grid(T, (H + nw - 1) / nw, nsplit);
-  if (f32) {
-    auto k = latent_attention_kernel<float>;
-    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
-    k<<<grid, nw * 32, smem, s>>>((const float*)q, (const float*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R, page, scale,
-                                  inv_freq, (float*)out, nsplit, chunk, part);
-    if (nsplit > 1) latent_combine_kernel<float><<<T * H, 128, 0, s>>>(part, sink, H, L, nsplit, (float*)out);
-  } else {
-    auto k = latent_attention_kernel<__nv_bfloat16>;
-    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
-    k<<<grid, nw * 32, smem, s>>>((const __nv_bfloat16*)q, (const __nv_bfloat16*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R,
-                                  page, scale, inv_freq, (__nv_bfloat16*)out, nsplit, chunk, part);
-    if (nsplit > 1) latent_combine_kernel<__nv_bfloat16><<<T * H, 128, 0, s>>>(part, sink, H, L, nsplit, (__nv_bfloat16*)out);
-  }
+#define LAT_LAUNCH(AT_, VEC_)                                                                                                          \
+  do {                                                                                                                                 \
+    auto k = latent_attention_kernel<AT_, VEC_>;                                                                                       \
+    if (smem > 48 * 1024) {                                                                                                            \
+      cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                 \
+      if (e != cudaSuccess) return e;                                                                                                  \
+    }                                                                                                                                  \
+    k<<<grid, nw * 32, smem, s>>>((const AT_*)q, (const AT_*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R, page, scale, \
+                                  inv_freq, (AT_*)out, nsplit, chunk, part);                                                           \
+    if (nsplit > 1) latent_combine_kernel<AT_><<<T * H, 128, 0, s>>>(part, sink, H, L, nsplit, (AT_*)out);                             \
+  } while (0)
+  if (f32) { if (vec) LAT_LAUNCH(float, true); else LAT_LAUNCH(float, false); }
+  else { if (vec) LAT_LAUNCH(__nv_bfloat16, true); else LAT_LAUNCH(__nv_bfloat16, false); }
+#undef LAT_LAUNCH
   return last();
 }
 

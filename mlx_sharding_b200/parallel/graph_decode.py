@@ -338,8 +338,18 @@ class DecodeGraphCache:
             g = torch.cuda.CUDAGraph()
             torch.cuda.synchronize()
             n0 = _b.C().launch_count()
-            with torch.cuda.graph(g):
-                e.out = self.body(e)
+            # no garbage collection inside the capture: a collector run that destroys CUDA objects of older engines (graphs, events)
+            # is an unsafe call under global capture mode and invalidates the capture in progress
+            import gc
+
+            gc_was = gc.isenabled()
+            gc.disable()
+            try:
+                with torch.cuda.graph(g):
+                    e.out = self.body(e)
+            finally:
+                if gc_was:
+                    gc.enable()
             e.launches = _b.C().launch_count() - n0
             e.graph = g
             self.captures += 1

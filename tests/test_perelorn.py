@@ -26,6 +26,9 @@ MAMBA = dict(type="mamba2", mixer=dict(conv=4, groups=1, heads=3, norm_groups=3,
 MAMBA_G = dict(type="mamba2", mixer=dict(conv=2, groups=2, heads=4, norm_groups=1, state=24, vdim=8), mlp=dict(ff=96, kind="dense"))
 ATTN = dict(type="latent_attention", mixer=dict(dim=24, heads=3, kv_rank=40, q_rank=32, rot=dict(base=5000.0, dims=16), rot_dim=16,
                                                 scale=0.2, vdim=8), mlp=dict(ff=80, kind="dense"))
+# kv_rank a multiple of 128 (the kernels' 16-byte path) and more heads than one CTA's warps
+ATTN_WIDE = dict(type="latent_attention", mixer=dict(dim=8, heads=9, kv_rank=256, q_rank=16, rot=dict(base=300.0, dims=8), rot_dim=8,
+                                                     scale=0.3, vdim=8), mlp=None)
 LIGHT = dict(type="lightning", mixer=dict(decay=[0.5, 0.97], dim=16, heads=2, vdim=24), mlp=None)
 
 
@@ -65,7 +68,7 @@ def close(a, b, tol):
     assert err < tol, f"relative error {err:.3e} >= {tol}"
 
 
-CASES = {"mamba2": [MAMBA], "mamba2_groups": [MAMBA_G], "latent": [ATTN], "lightning": [LIGHT], "stack": [MAMBA, ATTN, LIGHT, MAMBA_G, ATTN]}
+CASES = {"latent_wide": [ATTN_WIDE], "mamba2": [MAMBA], "mamba2_groups": [MAMBA_G], "latent": [ATTN], "lightning": [LIGHT], "stack": [MAMBA, ATTN, LIGHT, MAMBA_G, ATTN]}
 DEVICES = [pytest.param("cpu", torch.float32, 2e-4, id="cpu"),
            pytest.param("cuda", torch.float32, 2e-4, id="b200-f32", marks=pytest.mark.gpu),
            pytest.param("cuda", torch.bfloat16, 6e-2, id="b200-bf16", marks=pytest.mark.gpu)]
@@ -157,6 +160,19 @@ def test_far_key_and_sink_show(device, dtype, tol):
     nosink = copy.deepcopy(sd)
     nosink["l0.mix.sink"][:] = -1e4
     assert (oracle.forward(cfgd, nosink, t) - want).abs().max() > 1e-2
+
+
+@pytest.mark.parametrize("device,dtype,tol", DEVICES)
+def test_long_context_decode(device, dtype, tol):
+    """A 290-token prompt (the attention of a single long portion takes the matrix-product form on the GPU) and then single tokens
+    whose keys are split over several CTAs and merged with the sink."""
+    cfgd = make_cfg([ATTN_WIDE, LIGHT], side=0)
+    model, sd = make_model(cfgd, device, dtype, edit=lambda sd: sd["l0.mix.sink"].copy_(torch.linspace(-2, 3, 9)))
+    t = toks(296, seed=9)
+    want = oracle.forward(cfgd, sd, t)
+    s = session(model, pages=21)
+    got = [s.step([dict(id="r", tokens=t[:290], want=[0, 100, 289])])] + [s.step([dict(id="r", tokens=[x], want=[0])]) for x in t[290:]]
+    close(torch.cat(got), torch.cat([want[[0, 100, 289]], want[290:]]), tol)
 
 
 @pytest.mark.parametrize("device,dtype,tol", DEVICES)
