@@ -932,7 +932,7 @@ Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& si
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && pool.is_contiguous() && pool.dim() == 4 && pool.size(1) == 1 && pool.size(3) == q.size(2) &&
               pool.scalar_type() == q.scalar_type(), "q [T, H, kv_rank + rot], pool [pages, 1, page, kv_rank + rot]");
   const int64_t T = q.size(0), H = q.size(1), R = q.size(2) - L;
-  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && sink.numel() == H && L <= 512, "latent attention: kv_rank <= 512");
+  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && sink.numel() == H && L <= 1024, "latent attention: kv_rank <= 1024");
   const c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty({T, H, L}, q.options());
   if (T == 0) return out;

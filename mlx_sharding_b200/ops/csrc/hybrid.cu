@@ -319,11 +319,11 @@ __global__ void latent_prologue_kernel(const AT* __restrict__ x, long long ld_x,
 // Causal multi-query attention over the paged latent rows, with a sink: softmax denominator = exp(sink_h) + sum_j exp(s_j).
 // grid (T, ceil(H / warps)); one warp per head; key tiles of 32 rows staged in shared memory as fp32 and shared by the heads.
 constexpr int kLatTile = 32;
-constexpr int kLatMaxPerLane = 16;   // latent width <= 512
+constexpr int kLatMaxPerLane = 32;   // output registers per lane: 16 for a latent width <= 512, 32 up to 1024
 
 // VEC (kv_rank a multiple of 128, row width a multiple of 4): 16-byte shared-memory loads in both phases — lane l owns output dims
 // 4l + 128i .. +3 — and key rows padded to a multiple of 4 floats; otherwise scalar loads, lane l owns dims l + 32i, rows padded by 1.
-template <typename AT, bool VEC>
+template <typename AT, bool VEC, int NPL>
 __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __restrict__ pool, const float* __restrict__ sink,
                                         const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ positions,
                                         const int* __restrict__ cu, int B, int H, int L, int R, int page, float scale,
@@ -358,9 +358,9 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
   }
   // the sink: one extra term exp(sink - m) of the denominator, no key, no value (added by the combine kernel when keys are split)
   float m = nsplit > 1 ? -INFINITY : (h < H ? sink[h] : 0.f), l = nsplit > 1 ? 0.f : 1.f;
-  float o[kLatMaxPerLane];
+  float o[NPL];
 #pragma unroll
-  for (int i = 0; i < kLatMaxPerLane; ++i) o[i] = 0.f;
+  for (int i = 0; i < NPL; ++i) o[i] = 0.f;
   const int nper = (L + 31) / 32;
   const float* qh = qs + warp * Dq;
   const int jend = min(pos + 1, (int)(blockIdx.z + 1) * chunk);
@@ -412,20 +412,20 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
     l = l * corr + warp_sum(pj);
     m = mn;
 #pragma unroll
-    for (int i = 0; i < kLatMaxPerLane; ++i) o[i] *= corr;
+    for (int i = 0; i < NPL; ++i) o[i] *= corr;
     for (int jj = 0; jj < nk; ++jj) {
       const float pv = __shfl_sync(0xffffffffu, pj, jj);
       const float* kr = ks + jj * ldk;
       if (VEC) {
 #pragma unroll
-        for (int i = 0; i < kLatMaxPerLane / 4; ++i)
+        for (int i = 0; i < NPL / 4; ++i)
           if (i < L / 128) {
             const float4 c = *reinterpret_cast<const float4*>(kr + 4 * lane + 128 * i);
             o[4 * i] += pv * c.x; o[4 * i + 1] += pv * c.y; o[4 * i + 2] += pv * c.z; o[4 * i + 3] += pv * c.w;
           }
       } else {
 #pragma unroll
-        for (int i = 0; i < kLatMaxPerLane; ++i)
+        for (int i = 0; i < NPL; ++i)
           if (i < nper) { const int d = lane + 32 * i; if (d < L) o[i] += pv * kr[d]; }
       }
     }
@@ -434,7 +434,7 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
   if (h < H && nsplit == 1) {
     const float inv = 1.f / l;
 #pragma unroll
-    for (int i = 0; i < kLatMaxPerLane; ++i) {
+    for (int i = 0; i < NPL; ++i) {
       const int d = VEC ? 4 * lane + 128 * (i / 4) + (i % 4) : lane + 32 * i;
       if (d < L) stf<AT>(out + ((long long)t * H + h) * L + d, o[i] * inv);
     }
@@ -442,7 +442,7 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
     float* pp = part + (((long long)t * H + h) * nsplit + blockIdx.z) * (L + 2);
     if (lane == 0) { pp[0] = m; pp[1] = l; }
 #pragma unroll
-    for (int i = 0; i < kLatMaxPerLane; ++i) {
+    for (int i = 0; i < NPL; ++i) {
       const int d = VEC ? 4 * lane + 128 * (i / 4) + (i % 4) : lane + 32 * i;
       if (d < L) pp[2 + d] = o[i];
     }
@@ -634,7 +634,7 @@ cudaError_t latent_attention_launch(const void* q, const void* pool, const float
   dim3 grid(T, (H + nw - 1) / nw, nsplit);
 #define LAT_LAUNCH(AT_, VEC_)                                                                                                          \
   do {                                                                                                                                 \
-    auto k = latent_attention_kernel<AT_, VEC_>;                                                                                       \
+    auto k = L <= 512 ? latent_attention_kernel<AT_, VEC_, 16> : latent_attention_kernel<AT_, VEC_, 32>;                               \
     if (smem > 48 * 1024) {                                                                                                            \
       cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);                                 \
       if (e != cudaSuccess) return e;                                                                                                  \

@@ -29,6 +29,11 @@ ATTN = dict(type="latent_attention", mixer=dict(dim=24, heads=3, kv_rank=40, q_r
 # kv_rank a multiple of 128 (the kernels' 16-byte path) and more heads than one CTA's warps
 ATTN_WIDE = dict(type="latent_attention", mixer=dict(dim=8, heads=9, kv_rank=256, q_rank=16, rot=dict(base=300.0, dims=8), rot_dim=8,
                                                      scale=0.3, vdim=8), mlp=None)
+# latent wider than 512: the kernels' second register budget, with and without the 16-byte path
+ATTN_XL = dict(type="latent_attention", mixer=dict(dim=8, heads=2, kv_rank=640, q_rank=8, rot=dict(base=50.0, dims=4), rot_dim=4,
+                                                   scale=0.2, vdim=8), mlp=None)
+ATTN_XL_ODD = dict(type="latent_attention", mixer=dict(dim=8, heads=2, kv_rank=522, q_rank=8, rot=dict(base=50.0, dims=6), rot_dim=6,
+                                                       scale=0.2, vdim=8), mlp=None)
 LIGHT = dict(type="lightning", mixer=dict(decay=[0.5, 0.97], dim=16, heads=2, vdim=24), mlp=None)
 
 
@@ -68,7 +73,7 @@ def close(a, b, tol):
     assert err < tol, f"relative error {err:.3e} >= {tol}"
 
 
-CASES = {"latent_wide": [ATTN_WIDE], "mamba2": [MAMBA], "mamba2_groups": [MAMBA_G], "latent": [ATTN], "lightning": [LIGHT], "stack": [MAMBA, ATTN, LIGHT, MAMBA_G, ATTN]}
+CASES = {"latent_xl": [ATTN_XL, ATTN_XL_ODD], "latent_wide": [ATTN_WIDE], "mamba2": [MAMBA], "mamba2_groups": [MAMBA_G], "latent": [ATTN], "lightning": [LIGHT], "stack": [MAMBA, ATTN, LIGHT, MAMBA_G, ATTN]}
 DEVICES = [pytest.param("cpu", torch.float32, 2e-4, id="cpu"),
            pytest.param("cuda", torch.float32, 2e-4, id="b200-f32", marks=pytest.mark.gpu),
            pytest.param("cuda", torch.bfloat16, 6e-2, id="b200-bf16", marks=pytest.mark.gpu)]
