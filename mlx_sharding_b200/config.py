@@ -21,7 +21,7 @@ MODEL_REMAPPING = {
     "mistral": "llama",  # reference utils.py:15
 }
 
-SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn")
+SUPPORTED_ARCHS = ("llama", "gemma2", "deepseek_v2", "perelorn", "gusolorn")
 
 
 @dataclass(frozen=True)
@@ -161,6 +161,8 @@ class ModelConfig:
         d = dict(d)
         if "model_type" not in d and str(d.get("architecture", "")).lower() == "perelorn":
             d = _perelorn_flat(d)
+        elif "model_type" not in d and str(d.get("architecture", "")).lower() == "gusolorn":
+            d = _gusolorn_flat(d)
         mt = d.get("model_type", "llama")
         if mt == "phi-msft":
             raise ValueError(
@@ -293,6 +295,52 @@ def perelorn_config(width=2048, vocab=32000, blocks=4, heads=16, ff=8192, side_d
                                               heads=heads, vdim=128), mlp=None)
     d = dict(architecture="Perelorn", layers=[mamba, attn, mamba, light] * blocks, logit_scale=1.0, norm=dict(eps=1e-5),
              token_side=dict(dim=side_dim), vocab=vocab, width=width)
+    d.update(overrides)
+    return d
+
+
+def _gusolorn_flat(d: Dict[str, Any]) -> Dict[str, Any]:
+    """Gusolorn's nested config.json (``layers`` = list of {type, mixer, mlp}; ``norm.eps``; ``vocab``; ``width``) -> the flat fields of
+    :class:`ModelConfig`.  Mixers: ``mlstm`` (heads, dim, vdim, gate_cap) and ``latent_attention`` (heads, dim, rot_dim, vdim, kv_rank,
+    scale, rot.{base,dims}, optional mask.size = sliding window, optional kv_from = layer whose cached rows it reads).  Feed-forwards:
+    ``dense`` (ff) or ``moe`` (router.{experts,top}, expert.{ff,limit}, optional shared.{ff,limit}).  Every size is read from the file."""
+    layers = [dict(type=str(L["type"]), mixer=dict(L["mixer"]), mlp=(dict(L["mlp"]) if L.get("mlp") else None)) for L in d["layers"]]
+    for i, L in enumerate(layers):
+        m = L["mixer"]
+        if L["type"] not in ("mlstm", "latent_attention"):
+            raise ValueError(f"Gusolorn: unknown mixer type '{L['type']}'")
+        if L["mlp"] is not None and L["mlp"].get("kind", "dense") not in ("dense", "moe"):
+            raise ValueError(f"Gusolorn: unknown feed-forward kind '{L['mlp'].get('kind')}'")
+        if L["type"] == "latent_attention":
+            if int(m["rot"]["dims"]) != int(m["rot_dim"]):
+                raise ValueError("Gusolorn latent attention: rot.dims must equal rot_dim")
+            src = m.get("kv_from")
+            if src is not None:
+                s = layers[int(src)] if 0 <= int(src) < i else None
+                if s is None or s["type"] != "latent_attention" or s["mixer"].get("kv_from") is not None:
+                    raise ValueError(f"Gusolorn layer {i}: kv_from must name an earlier latent-attention layer with its own down-projection")
+                sm = s["mixer"]
+                if (int(sm["kv_rank"]), int(sm["rot_dim"]), float(sm["rot"]["base"])) != (int(m["kv_rank"]), int(m["rot_dim"]), float(m["rot"]["base"])):
+                    raise ValueError(f"Gusolorn layer {i}: kv_from layer has another latent width or rotation")
+    out = {k: v for k, v in d.items() if k not in ("architecture", "layers", "norm", "vocab", "width")}
+    ff = [L["mlp"]["ff"] if L["mlp"].get("kind", "dense") == "dense" else L["mlp"]["expert"]["ff"] for L in layers if L["mlp"]]
+    out.update(model_type="gusolorn", hidden_size=int(d["width"]), vocab_size=int(d["vocab"]), num_hidden_layers=len(layers),
+               rms_norm_eps=float(d["norm"]["eps"]), layer_specs=layers, intermediate_size=int(max(ff)) if ff else 0,
+               num_attention_heads=int(max(L["mixer"]["heads"] for L in layers)))
+    return out
+
+
+def gusolorn_config(width=2048, vocab=32000, blocks=2, heads=16, ff=8192, experts=16, top=2, expert_ff=1024, window=1024, **overrides) -> Dict[str, Any]:
+    """A Gusolorn config.json with layer sizes that resemble a real model: ``blocks`` x (latent attention + dense feed-forward, mLSTM
+    + mixture of experts, mLSTM + mixture of experts, latent attention reading the first layer's rows + mixture of experts)."""
+    att = dict(dim=128, heads=heads, kv_rank=512, rot=dict(base=10000.0, dims=64), rot_dim=64, scale=192 ** -0.5, vdim=128, mask=dict(size=window))
+    moe = dict(kind="moe", router=dict(experts=experts, top=top), expert=dict(ff=expert_ff, limit=7.0), shared=dict(ff=expert_ff, limit=7.0))
+    ml = dict(type="mlstm", mixer=dict(dim=128, heads=heads, vdim=128, gate_cap=15.0), mlp=moe)
+    layers = []
+    for b in range(blocks):
+        layers += [dict(type="latent_attention", mixer=dict(att), mlp=dict(ff=ff, kind="dense")), ml, ml,
+                   dict(type="latent_attention", mixer=dict(att, kv_from=4 * b), mlp=moe)]
+    d = dict(architecture="Gusolorn", layers=layers, norm=dict(eps=1e-5), vocab=vocab, width=width)
     d.update(overrides)
     return d
 

@@ -183,7 +183,8 @@ class HybridCache(PagedKVCache):
     """Cache of a model whose layers keep different things between steps: paged pools for attention layers (any row width, one
     pool per layer: ``k[li]``; ``v[li]`` is an empty tensor when the values are read out of the key rows) and per-sequence *state
     slots* for recurrent layers (``state[li]`` = dict name -> ``[num_slots, ...]`` tensor).  ``layout`` lists the local layers:
-    ``("paged", row_width, dtype)`` or ``("state", {name: (shape, dtype)})``.  Pages and slots are managed on the host by
+    ``("paged", row_width, dtype)``, ``("state", {name: (shape, dtype)})`` or ``("alias", j)`` (the layer keeps nothing of its own and
+    reads local layer ``j``'s pool, which comes earlier in the list: cross-layer sharing of cached rows).  Pages and slots are managed on the host by
     :class:`SequenceTable`; the step metadata carries block tables and slot ids."""
 
     def __init__(self, layout, num_pages: int, page_size: int, num_slots: int, device="cpu"):
@@ -191,7 +192,13 @@ class HybridCache(PagedKVCache):
         self.kv_heads, self.d_k, self.d_v = 1, 0, 0
         self.k, self.v, self.state = [], [], []
         for ent in layout:
-            if ent[0] == "paged":
+            if ent[0] == "alias":
+                if not (0 <= ent[1] < len(self.k)) or self.k[ent[1]] is None:
+                    raise ValueError("cache layout: an alias must name an earlier paged layer")
+                self.k.append(self.k[ent[1]])
+                self.v.append(self.v[ent[1]])
+                self.state.append(None)
+            elif ent[0] == "paged":
                 self.k.append(torch.zeros(num_pages, 1, page_size, ent[1], dtype=ent[2], device=device))
                 self.v.append(torch.empty(0, dtype=ent[2], device=device))
                 self.state.append(None)
@@ -201,7 +208,8 @@ class HybridCache(PagedKVCache):
                 self.state.append({n: torch.zeros(num_slots, *shape, dtype=dt, device=device) for n, (shape, dt) in ent[1].items()})
 
     def nbytes(self) -> int:
-        ts = [t for t in self.k if t is not None] + [t for d in self.state if d for t in d.values()]
+        ts = {id(t): t for t in self.k if t is not None}          # aliased pools count once
+        ts = list(ts.values()) + [t for d in self.state if d for t in d.values()]
         return sum(t.numel() * t.element_size() for t in ts)
 
 

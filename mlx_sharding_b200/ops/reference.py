@@ -441,27 +441,41 @@ def _rot_half(v: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> tor
     return torch.cat([u1 * c - u2 * s, u2 * c + u1 * s, v[..., 2 * half:]], -1)
 
 
-def latent_kv_prologue(dqkv: torch.Tensor, q_rank: int, kv_rank: int, qn_w: torch.Tensor, kvn_w: torch.Tensor, eps: float,
-                       pool: torch.Tensor, meta: BatchMeta, inv_freq: torch.Tensor) -> torch.Tensor:
-    """Rows ``[c_q raw: q_rank | c raw: kv_rank | k_rot raw]`` -> returns ``RMSnorm(c_q) * qn_w``; appends ``[RMSnorm(c) * kvn_w |
-    rotate_half(k_rot)]`` to the paged latent pool ``[pages, 1, page, kv_rank + rot]`` at ``meta.slot_mapping``."""
-    cq = rmsnorm_cast(dqkv[:, :q_rank], qn_w, eps, dqkv.dtype)
+def _rot_pairs(v: torch.Tensor, pos: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """Adjacent pairs ``(2i, 2i+1)`` of the first ``2 * len(inv_freq)`` entries turn by ``pos * inv_freq[i]``."""
+    half = inv_freq.numel()
+    a = pos.float()[:, None] * inv_freq.float()
+    c, s = torch.cos(a), torch.sin(a)
+    while c.dim() < v.dim():
+        c, s = c.unsqueeze(1), s.unsqueeze(1)
+    u1, u2 = v[..., 0:2 * half:2], v[..., 1:2 * half:2]
+    rot = torch.stack([u1 * c - u2 * s, u2 * c + u1 * s], -1).flatten(-2)
+    return torch.cat([rot, v[..., 2 * half:]], -1)
+
+
+def latent_kv_prologue(dqkv: torch.Tensor, q_rank: int, kv_rank: int, qn_w: Optional[torch.Tensor], kvn_w: torch.Tensor, eps: float,
+                       pool: torch.Tensor, meta: BatchMeta, inv_freq: torch.Tensor, interleaved: bool = False) -> Optional[torch.Tensor]:
+    """Rows ``[c_q raw: q_rank | c raw: kv_rank | k_rot raw]`` -> returns ``RMSnorm(c_q) * qn_w`` (``None`` when ``q_rank`` is 0: the
+    design has no query latent); appends ``[RMSnorm(c) * kvn_w | rotate(k_rot)]`` to the paged latent pool ``[pages, 1, page, kv_rank +
+    rot]`` at ``meta.slot_mapping``.  ``interleaved``: rotary pairs are ``(2i, 2i+1)`` instead of ``(i, i + rot/2)``."""
+    cq = rmsnorm_cast(dqkv[:, :q_rank], qn_w, eps, dqkv.dtype) if q_rank else None
     c = rmsnorm_cast(dqkv[:, q_rank:q_rank + kv_rank], kvn_w, eps, torch.float32)
-    kr = _rot_half(dqkv[:, q_rank + kv_rank:].float(), meta.positions, inv_freq)
+    kr = (_rot_pairs if interleaved else _rot_half)(dqkv[:, q_rank + kv_rank:].float(), meta.positions, inv_freq)
     flat = pool.view(-1, pool.shape[-1])
     flat[meta.slot_mapping.long()] = torch.cat([c, kr], -1).to(pool.dtype)
     return cq
 
 
-def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: torch.Tensor, meta: BatchMeta, scale: float, kv_rank: int,
-                     inv_freq: torch.Tensor, out_dtype: torch.dtype = torch.float32) -> torch.Tensor:
+def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: Optional[torch.Tensor], meta: BatchMeta, scale: float, kv_rank: int,
+                     inv_freq: torch.Tensor, out_dtype: torch.dtype = torch.float32, window: int = 0, interleaved: bool = False) -> torch.Tensor:
     """Causal multi-query attention over the cached latent rows with a *sink* in the softmax.  ``q`` ``[T, H, kv_rank + rot]`` (latent
     part already multiplied by the key up-projection; the rot part is rotated here), keys = pool rows, values = their first
-    ``kv_rank`` entries; ``p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i))``.  Returns fp32 ``[T, H, kv_rank]``."""
+    ``kv_rank`` entries; ``p_j = exp(s_j) / (exp(sink_h) + sum_i exp(s_i))`` (``sink=None``: the ordinary softmax).  ``window > 0``: the
+    query at position ``i`` sees keys ``j`` with ``0 <= i - j < window``.  Returns fp32 ``[T, H, kv_rank]``."""
     T, H, Dq = q.shape
     page = pool.shape[2]
     qf = q.float()
-    qf = torch.cat([qf[..., :kv_rank], _rot_half(qf[..., kv_rank:], meta.positions, inv_freq)], -1)
+    qf = torch.cat([qf[..., :kv_rank], (_rot_pairs if interleaved else _rot_half)(qf[..., kv_rank:], meta.positions, inv_freq)], -1)
     out = torch.empty(T, H, kv_rank, dtype=torch.float32, device=q.device)
     bt = meta.block_tables.long()
     for b, (s, e, c0, _) in enumerate(_seq_ranges(meta)):
@@ -469,10 +483,16 @@ def latent_attention(q: torch.Tensor, pool: torch.Tensor, sink: torch.Tensor, me
         idx = torch.arange(n, device=q.device)
         rows = pool.view(-1, Dq)[bt[b, idx // page] * page + idx % page].float()               # [n, Dq]
         sc = torch.einsum("thd,nd->thn", qf[s:e], rows) * scale
-        mask = idx[None, :] > (c0 + torch.arange(e - s, device=q.device))[:, None]
+        qpos = (c0 + torch.arange(e - s, device=q.device))[:, None]
+        mask = idx[None, :] > qpos
+        if window > 0:
+            mask = mask | (idx[None, :] <= qpos - window)
         sc = sc.masked_fill(mask[:, None, :], float("-inf"))
-        sk = sink.float().view(1, H, 1).expand(e - s, H, 1)
-        p = torch.softmax(torch.cat([sc, sk], -1), -1)[..., :n]
+        if sink is None:
+            p = torch.softmax(sc, -1)
+        else:
+            sk = sink.float().view(1, H, 1).expand(e - s, H, 1)
+            p = torch.softmax(torch.cat([sc, sk], -1), -1)[..., :n]
         out[s:e] = torch.einsum("thn,nd->thd", p, rows[:, :kv_rank])
     return out.to(out_dtype)
 
@@ -487,6 +507,106 @@ def linear_any(x: torch.Tensor, W: LinearWeight, out_dtype: torch.dtype, act: st
     return y.to(out_dtype)
 
 
-def latent_attention_prefill(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=torch.float32):
+def latent_attention_prefill(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=torch.float32, window: int = 0,
+                             interleaved: bool = False):
     """Single-sequence prefill form of :func:`latent_attention` (the CUDA backend runs it as two GEMMs); same math here."""
-    return latent_attention(q, pool, sink, meta, scale, kv_rank, inv_freq, out_dtype)
+    return latent_attention(q, pool, sink, meta, scale, kv_rank, inv_freq, out_dtype, window, interleaved)
+
+
+def scaled_add_norm_(x: torch.Tensor, y: torch.Tensor, ls: Optional[torch.Tensor], w: torch.Tensor, eps: float, act_dtype: torch.dtype,
+                     extra: Optional[torch.Tensor] = None, extra_gate: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pre-norm residual step on the fp32 stream ``x`` (in place): ``x += (y + extra * sigmoid(extra_gate)) * ls`` (``ls``: per-channel
+    layer scale or ``None``; ``extra`` / ``extra_gate``: an always-on branch with one gate logit per row), then returns
+    ``x / sqrt(mean(x^2) + eps) * w`` in the activation dtype: the input of the sublayer that follows."""
+    yf = y.float()
+    if extra is not None:
+        yf = yf + extra.float() * torch.sigmoid(extra_gate.float()).reshape(-1, 1)
+    x += yf * ls.float() if ls is not None else yf
+    return rmsnorm_cast(x, w, eps, act_dtype)
+
+
+def mlstm_col_block(vdim: int) -> int:
+    """Value columns of a head that one CTA of the mLSTM scan owns (fixed per size, so the per-block copies of the normaliser state
+    keep their meaning from step to step)."""
+    pb = int(vdim)
+    while pb > 32 and pb % 2 == 0:
+        pb //= 2
+    return pb
+
+
+def mlstm_scan(qkv: torch.Tensor, gates: torch.Tensor, gate_bias: torch.Tensor, state: dict, meta: BatchMeta, heads: int, dim: int,
+               vdim: int, cap: float, q_scale: float) -> torch.Tensor:
+    """Matrix-memory recurrence with exponential gating and a running maximum (fp32), per head:
+    ``i = cap tanh((gi + bi) / cap)``, ``f = logsigmoid(cap tanh((gf + bf) / cap))``, ``m' = max(f + m, i)``,
+    ``S <- e^(f + m - m') S + e^(i - m') k v^T``, ``n`` likewise with ``k``, ``o = S^T q / (max(|n . q|, e^(-m')) + 1e-6)``; ``m, S, n``
+    start at zero.  ``qkv`` columns ``[q: heads*dim | k: heads*dim | v: heads*vdim | ...]`` (``q`` is multiplied by ``q_scale``),
+    ``gates`` fp32 ``[T, >= 2*heads]`` = raw ``[gi | gf]``, ``gate_bias`` fp32 ``[2*heads]``.  ``state``: ``S`` ``[slots, heads, dim,
+    vdim]``, ``n`` ``[slots, heads, vdim / col_block, dim]``, ``m`` ``[slots, heads, vdim / col_block]`` (one copy of ``n, m`` per
+    column block).  Returns fp32 ``[T, heads*vdim]``."""
+    T, H = qkv.shape[0], heads
+    q = qkv[:, :H * dim].float().view(T, H, dim) * q_scale
+    k = qkv[:, H * dim:2 * H * dim].float().view(T, H, dim)
+    v = qkv[:, 2 * H * dim:2 * H * dim + H * vdim].float().view(T, H, vdim)
+    g = gates[:, :2 * H].float() + gate_bias.float()
+    ig = cap * torch.tanh(g[:, :H] / cap)
+    fg = F.logsigmoid(cap * torch.tanh(g[:, H:] / cap))
+    o = torch.empty(T, H, vdim, dtype=torch.float32, device=qkv.device)
+    for s, e, c0, slot in _seq_ranges(meta):
+        if e == s:
+            continue
+        if c0 > 0:
+            S, n, m = state["S"][slot].clone(), state["n"][slot][:, 0].clone(), state["m"][slot][:, 0].clone()
+        else:
+            S, n, m = torch.zeros_like(state["S"][slot]), torch.zeros_like(state["n"][slot][:, 0]), torch.zeros_like(state["m"][slot][:, 0])
+        for t in range(s, e):
+            mn = torch.maximum(fg[t] + m, ig[t])
+            a, b = torch.exp(fg[t] + m - mn), torch.exp(ig[t] - mn)
+            S = a[:, None, None] * S + (b[:, None] * k[t])[:, :, None] * v[t][:, None, :]
+            n = a[:, None] * n + b[:, None] * k[t]
+            m = mn
+            den = torch.maximum((n * q[t]).sum(-1).abs(), torch.exp(-m)) + 1e-6
+            o[t] = torch.einsum("hdv,hd->hv", S, q[t]) / den[:, None]
+        state["S"][slot] = S
+        state["n"][slot] = n[:, None, :].expand_as(state["n"][slot])
+        state["m"][slot] = m[:, None].expand_as(state["m"][slot])
+    return o.view(T, H * vdim)
+
+
+def sigmoid_topk(z: torch.Tensor, num_experts: int, top: int) -> Tuple[torch.Tensor, torch.Tensor]:
+    """Router on fp32 logits ``z[:, :num_experts]``: scores ``sigmoid(z)``, the ``top`` largest (ties: lowest id), weights = the chosen
+    scores as they are.  Returns ``(idx int32 [T, top], w fp32 [T, top])``."""
+    sc = torch.sigmoid(z[:, :num_experts].float())
+    order = torch.sort(sc, dim=-1, descending=True, stable=True).indices[:, :top]
+    return order.to(torch.int32), torch.gather(sc, 1, order)
+
+
+def clamped_glu(gu: torch.Tensor, limit: float, out_dtype: torch.dtype, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """``[g | u]`` ``[R, 2F]`` -> ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(s g, limit)``, ``u' = clamp(s u, +-limit)``; ``s`` =
+    ``row_scale`` (per row, default 1): scaling a linear projection's output equals scaling its input."""
+    Fh = gu.shape[1] // 2
+    g, u = gu[:, :Fh].float(), gu[:, Fh:].float()
+    if row_scale is not None:
+        g, u = g * row_scale.float()[:, None], u * row_scale.float()[:, None]
+    g, u = g.clamp(max=limit), u.clamp(-limit, limit)
+    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)).to(out_dtype)
+
+
+def moe_clamped_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wgu: LinearWeight, Wd: LinearWeight, limit: float) -> torch.Tensor:
+    """``y[t] = sum_j expert_{idx[t,j]}(w[t,j] x[t])`` with clamped-GLU experts (:func:`clamped_glu`): the router weight scales the
+    expert's INPUT.  ``Wgu`` ``[E, 2F, K]`` (gate rows then up rows), ``Wd`` ``[E, K, F]``.  Returns fp32 ``[T, K]``."""
+    T, k = idx.shape
+    y = torch.zeros(T, Wd.weight.shape[1], dtype=torch.float32, device=x.device)
+    il = idx.long()
+    for e in range(Wgu.weight.shape[0]):
+        tok, slot = torch.where(il == e)
+        if tok.numel() == 0:
+            continue
+        gu = x[tok].float() @ Wgu.weight[e].float().t()
+        h = clamped_glu(gu.to(x.dtype), limit, x.dtype, w[tok, slot])
+        y.index_add_(0, tok, h.float() @ Wd.weight[e].float().t())
+    return y
+
+
+def router_logits(x: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """fp32 router product ``x W^T`` (``w`` fp32 ``[rows, K]``; ``x`` in the activation dtype is widened, never the weight narrowed)."""
+    return x.float() @ w.float().t()

@@ -95,7 +95,7 @@ def key_in_shard(key: str, spec: ShardSpec, tied_embeddings: bool = False, model
     """True if checkpoint tensor ``key`` belongs to stage ``spec`` (half-layer boundaries included)."""
     if "rotary_emb.inv_freq" in key:
         return False
-    if model_type == "perelorn":       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
+    if model_type in ("perelorn", "gusolorn"):       # keys: embed, side.embed, l<i>.*, final.norm, head (single-stage model: everything or a layer range)
         m = re.match(r"l(\d+)\.", key)
         if m:
             return spec.owns_layer(int(m.group(1)))
@@ -252,6 +252,9 @@ def random_state_dict(cfg: ModelConfig, spec: Optional[ShardSpec] = None, dtype=
     if cfg.model_type == "perelorn":
         yield from _perelorn_random(cfg, gen, dtype, device, seed)
         return
+    if cfg.model_type == "gusolorn":
+        yield from _gusolorn_random(cfg, gen, dtype, device, seed)
+        return
     H = cfg.hidden_size
     q = quantization
     tied = cfg.tie_word_embeddings
@@ -386,6 +389,63 @@ def _perelorn_random(cfg: ModelConfig, gen, dtype, device, seed: int):
             yield p + "side.proj", lin(W, sd)
             yield p + "side.norm", vec(W)
     yield "final.norm", vec(W)
+    yield "head", lin(cfg.vocab_size, W)
+
+
+def _gusolorn_random(cfg: ModelConfig, gen, dtype, device, seed: int):
+    """Random-init Gusolorn tensors (checkpoint names and shapes of that design; norm weights stored around zero, layer scales around one,
+    gate rows large enough that the gate cap and the running maximum of the mLSTM matter)."""
+    gen.manual_seed(seed * 1000003 + 29)
+    W = cfg.hidden_size
+    rn = lambda *shape, std=1.0: torch.randn(*shape, generator=gen, device=device, dtype=torch.float32) * std
+    lin = lambda o, i, gain=1.0: (rn(o, i) * gain / (i ** 0.5)).to(dtype)
+    zc = lambda n: (0.1 * rn(n)).to(dtype)
+    vec = lambda n: (1.0 + 0.1 * rn(n)).to(dtype)
+    yield "embed", rn(cfg.vocab_size, W).to(dtype)
+    for i, L in enumerate(cfg.layer_specs):
+        p, m = f"l{i}.", L["mixer"]
+        yield p + "norm1", zc(W)
+        yield p + "ls1", vec(W)
+        if L["type"] == "mlstm":
+            H, D, V = m["heads"], m["dim"], m["vdim"]
+            for n, o in (("q", H * D), ("k", H * D), ("v", H * V), ("g", H * V)):
+                yield p + "mix." + n, lin(o, W)
+            yield p + "mix.o", lin(W, H * V)
+            yield p + "mix.norm", vec(H * V)
+            yield p + "mix.i", lin(H, W, 3.0)
+            yield p + "mix.i.b", rn(H).to(dtype)
+            yield p + "mix.f", lin(H, W, 3.0)
+            yield p + "mix.f.b", (rn(H) + 3.0).to(dtype)
+        else:
+            H, D, R, V, Lr = m["heads"], m["dim"], m["rot_dim"], m["vdim"], m["kv_rank"]
+            yield p + "mix.q", lin(H * (D + R), W)
+            if m.get("kv_from") is None:
+                yield p + "mix.dkv", lin(Lr + R, W)
+                yield p + "mix.dkv.norm", vec(Lr)
+            yield p + "mix.uk", lin(H * D, Lr)
+            yield p + "mix.uv", lin(H * V, Lr)
+            yield p + "mix.o", lin(W, H * V)
+        mlp = L["mlp"]
+        if mlp:
+            yield p + "norm2", zc(W)
+            yield p + "ls2", vec(W)
+            if mlp.get("kind", "dense") == "dense":
+                yield p + "mlp.up", lin(mlp["ff"], W)
+                yield p + "mlp.down", lin(W, mlp["ff"])
+            else:
+                F = mlp["expert"]["ff"]
+                for e in range(mlp["router"]["experts"]):
+                    yield p + f"mlp.e{e}.gate", lin(F, W, 2.0)
+                    yield p + f"mlp.e{e}.up", lin(F, W, 2.0)
+                    yield p + f"mlp.e{e}.down", lin(W, F)
+                yield p + "mlp.router", lin(mlp["router"]["experts"], W, 3.0)
+                if mlp.get("shared"):
+                    Fs = mlp["shared"]["ff"]
+                    yield p + "mlp.shared.gate", lin(Fs, W, 2.0)
+                    yield p + "mlp.shared.up", lin(Fs, W, 2.0)
+                    yield p + "mlp.shared.down", lin(W, Fs)
+                    yield p + "mlp.shared.sg", lin(1, W)
+    yield "final.norm", zc(W)
     yield "head", lin(cfg.vocab_size, W)
 
 
