@@ -545,36 +545,113 @@ def decay_scan(qkv, decay, state, meta: BatchMeta, heads: int, dim: int, vdim: i
     return C().hy_decay_scan(qkv, decay, state, meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads), int(dim), int(vdim), int(meta.max_q_len))
 
 
-def latent_kv_prologue(dqkv, q_rank: int, kv_rank: int, qn_w, kvn_w, eps: float, pool, meta: BatchMeta, inv_freq):
-    return C().hy_latent_prologue(dqkv, int(q_rank), int(kv_rank), qn_w, kvn_w, float(eps), pool, meta.slot_mapping, meta.positions, inv_freq)
+def latent_kv_prologue(dqkv, q_rank: int, kv_rank: int, qn_w, kvn_w, eps: float, pool, meta: BatchMeta, inv_freq, interleaved: bool = False):
+    cq = C().hy_latent_prologue(dqkv, int(q_rank), int(kv_rank), qn_w, kvn_w, float(eps), pool, meta.slot_mapping, meta.positions, inv_freq,
+                                bool(interleaved))
+    return cq if q_rank else None
 
 
-def latent_attention(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None):
+def latent_attention(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None, window: int = 0,
+                     interleaved: bool = False):
     return C().hy_latent_attention(q, pool, sink, meta.block_tables, meta.positions, meta.cu_seqlens, float(scale), int(kv_rank), inv_freq,
-                                   int(meta.max_ctx_len))
+                                   int(meta.max_ctx_len), int(window), bool(interleaved))
 
 
-def latent_attention_prefill(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None):
+def latent_attention_prefill(q, pool, sink, meta: BatchMeta, scale: float, kv_rank: int, inv_freq, out_dtype=None, window: int = 0,
+                             interleaved: bool = False):
     """:func:`latent_attention` for a step that holds ONE sequence with many query rows (a prompt or a portion of one), as matrix
     products: gather the sequence's cached rows ``K`` ``[ctx, kv_rank + rot]`` from its pages, ``S = Q K^T`` (fp32 out), the
     masked softmax with the sink (``hy_sink_softmax``), ``out = P K[:, :kv_rank]``.  The two products run on the tensor cores
     (tcgen05 GEMM; cuBLAS fp32 in exact mode); query rows are processed in blocks so the score matrix stays below 256 MB."""
     T, H, Dq = q.shape
     ctx, page = int(meta.max_ctx_len), pool.shape[2]
-    ctx0, npad = ctx - T, (ctx + 7) // 8 * 8
+    ctx0 = ctx - T
+    # with a sliding window only keys from position ``lo`` on are ever seen by this step's queries; row i of K is position lo + i
+    lo = max(0, ctx0 - window + 1) // 8 * 8 if window > 0 else 0
+    nk, npad = ctx - lo, (ctx - lo + 7) // 8 * 8
     pages = meta.block_tables[0, :(ctx + page - 1) // page].long()
-    ids = (pages[:, None] * page + torch.arange(page, device=q.device)).reshape(-1)[:ctx]
-    if npad > ctx:
-        ids = torch.cat([ids, ids[:1].expand(npad - ctx)])           # padding columns: any finite row (their probability is 0)
+    ids = (pages[:, None] * page + torch.arange(page, device=q.device)).reshape(-1)[lo:ctx]
+    if npad > nk:
+        ids = torch.cat([ids, ids[:1].expand(npad - nk)])            # padding columns: any finite row (their probability is 0)
     K = gather_rows(pool.view(-1, Dq), ids.contiguous(), 0, Dq, q.dtype)
-    Wk, Wc = LinearWeight(weight=K), LinearWeight(weight=K[:, :kv_rank].t().contiguous())
-    C().hy_rotate_half_(q, meta.positions, inv_freq, int(kv_rank))
+    C().hy_rotate_half_(q, meta.positions, inv_freq, int(kv_rank), bool(interleaved))
     is32 = _is32(q.dtype)
     block = max(1, (1 << 26) // (npad * H))
+    if window > 0:
+        block = min(block, max(64, (window + 63) // 64 * 64))         # a block of queries sees at most block + window - 1 keys
     outs = []
     for t0 in range(0, T, block):
         n = min(T, t0 + block) - t0
+        # keys this block can see: positions [ka, kb) relative to ``lo``, both multiples of 8 (16-byte aligned rows and columns)
+        ka = max(0, ctx0 + t0 - window + 1 - lo) // 8 * 8 if window > 0 else 0
+        kb = min(npad, (ctx0 + t0 + n - lo + 7) // 8 * 8)
+        Kb = K[ka:kb]
+        Wk, Wc = LinearWeight(weight=Kb), LinearWeight(weight=Kb[:, :kv_rank].t().contiguous())
         s = linear_any(q[t0:t0 + n].reshape(n * H, Dq), Wk, torch.float32)
-        p = C().hy_sink_softmax(s, sink, int(H), int(ctx0 + t0), float(scale), is32)
+        p = C().hy_sink_softmax(s, sink, int(H), int(ctx0 + t0), float(scale), is32, int(window), int(lo + ka))
         outs.append(linear_any(p, Wc, q.dtype).view(n, H, kv_rank))
     return outs[0] if len(outs) == 1 else torch.cat(outs)
+
+
+# ---- pre-norm residual step, mLSTM, sigmoid router and clamped-GLU experts (same functions as in ``ops/reference.py``)
+from .reference import mlstm_col_block  # noqa: E402,F401  (a pure function of the value width: shared by both backends and the cache layout)
+
+
+def scaled_add_norm_(x, y, ls, w, eps: float, act_dtype, extra=None, extra_gate=None):
+    return C().hy_scaled_add_norm_(x, y, ls, w, float(eps), _is32(act_dtype), extra, extra_gate)
+
+
+def mlstm_scan(qkv, gates, gate_bias, state: dict, meta: BatchMeta, heads: int, dim: int, vdim: int, cap: float, q_scale: float):
+    return C().hy_mlstm_scan(qkv, gates, gate_bias, state["S"], state["n"], state["m"], meta.cu_seqlens, meta.context_lens, _slots(meta), int(heads),
+                             int(dim), int(vdim), int(mlstm_col_block(vdim)), float(cap), float(q_scale), int(meta.max_q_len))
+
+
+def router_logits(x, w):
+    """fp32 router product (cuBLAS, TF32 off): the activations are widened, the fp32 weight is used as it is."""
+    return torch.nn.functional.linear(x.float(), w)
+
+
+def sigmoid_topk(z, num_experts: int, top: int):
+    idx, w = C().hy_sigmoid_topk(z, int(num_experts), int(top))
+    return idx, w
+
+
+def clamped_glu(gu, limit: float, out_dtype=None, row_scale=None):
+    return C().hy_clamped_glu(gu, float(limit), None, row_scale)
+
+
+def moe_clamped_experts(x, idx, w, Wgu: LinearWeight, Wd: LinearWeight, limit: float):
+    """Routed clamped-GLU experts, router weight on the expert's input (applied to the gate / up products, which are linear in it):
+    counting-sort permutation -> grouped gate|up GEMM -> clamped GLU -> grouped down GEMM (fp32) -> sum per token.  bf16 banks whose
+    sizes fit the grouped tcgen05 GEMM (rows multiples of 128, inner sizes multiples of 8) take it; exact mode (fp32) and other sizes
+    run one cuBLAS product per expert on the sorted rows."""
+    c = C()
+    T, k = idx.shape
+    wgu, wd = Wgu.weight, Wd.weight
+    E, F2, K = wgu.shape
+    if x.dtype == torch.bfloat16 and F2 % 128 == 0 and K % 128 == 0 and (F2 // 2) % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
+        offs, pair_row, xp = c.moe_permute(idx, x, E)
+        gu = c.grouped_linear(xp, wgu, None, offs, T, 0, False)
+        h = c.hy_clamped_glu(gu, float(limit), pair_row, w.reshape(-1))
+        y = c.grouped_linear(h, wd, None, offs, T, 0, True)
+        return c.hy_gather_sum(y, pair_row, int(k))
+    flat = idx.reshape(-1).long()
+    order = torch.sort(flat, stable=True).indices
+    pair_row = torch.empty_like(order, dtype=torch.int32)
+    pair_row[order] = torch.arange(order.numel(), device=x.device, dtype=torch.int32)
+    xp = gather_rows(x, (order // k).contiguous(), 0, K, x.dtype)
+    counts = torch.bincount(flat, minlength=E).tolist()
+    gu = torch.empty(xp.shape[0], F2, dtype=x.dtype, device=x.device)
+    r0 = 0
+    for e, n in enumerate(counts):
+        if n:
+            torch.matmul(xp[r0:r0 + n], wgu[e].t(), out=gu[r0:r0 + n])
+        r0 += n
+    h = c.hy_clamped_glu(gu, float(limit), pair_row, w.reshape(-1).contiguous())
+    y = torch.empty(xp.shape[0], K, dtype=torch.float32, device=x.device)
+    r0 = 0
+    for e, n in enumerate(counts):
+        if n:
+            y[r0:r0 + n] = torch.matmul(h[r0:r0 + n], wd[e].t()).float()
+        r0 += n
+    return c.hy_gather_sum(y, pair_row, int(k))

@@ -910,29 +910,36 @@ Tensor hy_decay_scan(const Tensor& qkv, const Tensor& decay, Tensor state, const
   return out;
 }
 
-Tensor hy_latent_prologue(const Tensor& x, int64_t Qr, int64_t L, const Tensor& qn_w, const Tensor& kvn_w, double eps, Tensor pool,
-                          const Tensor& slot_map, const Tensor& positions, const Tensor& inv_freq) {
-  check_act(x, "x"); check_rows(x, "x"); check_f32c(qn_w, "qn_w"); check_f32c(kvn_w, "kvn_w"); check_f32c(inv_freq, "inv_freq");
+Tensor hy_latent_prologue(const Tensor& x, int64_t Qr, int64_t L, const c10::optional<Tensor>& qn_w_, const Tensor& kvn_w, double eps, Tensor pool,
+                          const Tensor& slot_map, const Tensor& positions, const Tensor& inv_freq, bool interleaved) {
+  check_act(x, "x"); check_rows(x, "x"); check_f32c(kvn_w, "kvn_w"); check_f32c(inv_freq, "inv_freq");
   check_i32(slot_map, "slot_mapping"); check_i32(positions, "positions");
+  TORCH_CHECK(Qr == 0 || qn_w_.has_value(), "a query latent needs its norm weight");
+  const Tensor& qn_w = Qr > 0 ? *qn_w_ : kvn_w;      // Qr == 0: never read
+  if (Qr > 0) check_f32c(qn_w, "qn_w");
   const int64_t R = x.size(1) - Qr - L;
-  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && qn_w.numel() == Qr && kvn_w.numel() == L);
+  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && (Qr == 0 || qn_w.numel() == Qr) && kvn_w.numel() == L);
   TORCH_CHECK(pool.is_contiguous() && pool.scalar_type() == x.scalar_type() && pool.size(-1) == L + R, "latent pool must be [..., kv_rank + rot] of the activation type");
   const c10::cuda::CUDAGuard guard(x.device());
   Tensor cq = torch::empty({x.size(0), Qr}, x.options());
   LAUNCH_OK(b200::latent_prologue_launch(x.data_ptr(), x.stride(0), (int)Qr, (int)L, (int)R, qn_w.data_ptr<float>(), kvn_w.data_ptr<float>(), (float)eps,
                                          cq.data_ptr(), pool.data_ptr(), slot_map.data_ptr<int>(), positions.data_ptr<int>(), inv_freq.data_ptr<float>(),
-                                         is_f32(x), (int)x.size(0), cur_stream()));
+                                         is_f32(x), (int)x.size(0), interleaved ? 1 : 0, cur_stream()));
   return cq;
 }
 
-Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& sink, const Tensor& block_tables, const Tensor& positions,
-                           const Tensor& cu, double scale, int64_t L, const Tensor& inv_freq, int64_t max_ctx) {
-  check_act(q, "q"); check_f32c(sink, "sink"); check_f32c(inv_freq, "inv_freq"); check_i32(block_tables, "block_tables");
+Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const c10::optional<Tensor>& sink_, const Tensor& block_tables, const Tensor& positions,
+                           const Tensor& cu, double scale, int64_t L, const Tensor& inv_freq, int64_t max_ctx, int64_t window, bool interleaved) {
+  check_act(q, "q"); check_f32c(inv_freq, "inv_freq"); check_i32(block_tables, "block_tables");
+  if (sink_.has_value()) check_f32c(*sink_, "sink");
+  const float* sink_p = sink_.has_value() ? sink_->data_ptr<float>() : nullptr;
+  if (window > 0) max_ctx = std::min<int64_t>(max_ctx, window);       // keys that one query can see: what a key split divides
   check_i32(positions, "positions"); check_i32(cu, "cu_seqlens");
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && pool.is_contiguous() && pool.dim() == 4 && pool.size(1) == 1 && pool.size(3) == q.size(2) &&
               pool.scalar_type() == q.scalar_type(), "q [T, H, kv_rank + rot], pool [pages, 1, page, kv_rank + rot]");
   const int64_t T = q.size(0), H = q.size(1), R = q.size(2) - L;
-  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && sink.numel() == H && L <= 1024, "latent attention: kv_rank <= 1024");
+  TORCH_CHECK(R >= 0 && R % 2 == 0 && inv_freq.numel() == R / 2 && (!sink_.has_value() || sink_->numel() == H) && L <= 1024 && window >= 0,
+              "latent attention: kv_rank <= 1024");
   const c10::cuda::CUDAGuard guard(q.device());
   Tensor out = torch::empty({T, H, L}, q.options());
   if (T == 0) return out;
@@ -948,32 +955,111 @@ Tensor hy_latent_attention(const Tensor& q, const Tensor& pool, const Tensor& si
   Tensor part;
   if (nsplit > 1) part = torch::empty({T * H * nsplit * (L + 2)}, q.options().dtype(torch::kFloat32));
   else chunk = 1 << 30;
-  LAUNCH_OK(b200::latent_attention_launch(q.data_ptr(), pool.data_ptr(), sink.data_ptr<float>(), block_tables.data_ptr<int>(), (int)block_tables.size(1),
+  LAUNCH_OK(b200::latent_attention_launch(q.data_ptr(), pool.data_ptr(), sink_p, block_tables.data_ptr<int>(), (int)block_tables.size(1),
                                           positions.data_ptr<int>(), cu.data_ptr<int>(), (int)(cu.numel() - 1), (int)H, (int)L, (int)R, (int)pool.size(2),
                                           (float)scale, inv_freq.data_ptr<float>(), out.data_ptr(), is_f32(q), (int)T, (int)nsplit, (int)chunk,
-                                          nsplit > 1 ? part.data_ptr<float>() : nullptr, cur_stream()));
+                                          nsplit > 1 ? part.data_ptr<float>() : nullptr, (int)window, interleaved ? 1 : 0, cur_stream()));
   return out;
 }
 
 
-Tensor hy_rotate_half_(Tensor q, const Tensor& positions, const Tensor& inv_freq, int64_t L) {
+Tensor hy_rotate_half_(Tensor q, const Tensor& positions, const Tensor& inv_freq, int64_t L, bool interleaved) {
   check_act(q, "q"); check_i32(positions, "positions"); check_f32c(inv_freq, "inv_freq");
   TORCH_CHECK(q.dim() == 3 && q.is_contiguous() && (q.size(2) - L) == 2 * inv_freq.numel() && positions.numel() >= q.size(0));
   const c10::cuda::CUDAGuard guard(q.device());
   if (q.size(0) == 0) return q;
   LAUNCH_OK(b200::rotate_half_launch(q.data_ptr(), positions.data_ptr<int>(), inv_freq.data_ptr<float>(), (int)q.size(1), (int)L, (int)(q.size(2) - L),
-                                     is_f32(q), (int)q.size(0), cur_stream()));
+                                     is_f32(q), (int)q.size(0), interleaved ? 1 : 0, cur_stream()));
   return q;
 }
 
-Tensor hy_sink_softmax(const Tensor& s, const Tensor& sink, int64_t H, int64_t ctx0, double scale, bool out_f32) {
-  check_f32c(s, "scores"); check_f32c(sink, "sink");
-  TORCH_CHECK(s.dim() == 2 && sink.numel() == H && s.size(0) % H == 0);
+Tensor hy_sink_softmax(const Tensor& s, const c10::optional<Tensor>& sink, int64_t H, int64_t ctx0, double scale, bool out_f32, int64_t window,
+                       int64_t k0) {
+  check_f32c(s, "scores");
+  if (sink.has_value()) check_f32c(*sink, "sink");
+  TORCH_CHECK(s.dim() == 2 && (!sink.has_value() || sink->numel() == H) && s.size(0) % H == 0 && window >= 0 && k0 >= 0);
   const c10::cuda::CUDAGuard guard(s.device());
   Tensor out = torch::empty({s.size(0), s.size(1)}, s.options().dtype(act_type(out_f32)));
   if (s.size(0) == 0) return out;
-  LAUNCH_OK(b200::sink_softmax_launch(s.data_ptr<float>(), sink.data_ptr<float>(), (int)H, (int)s.size(1), (int)ctx0, (float)scale, out.data_ptr(), out_f32,
-                                      (long long)s.size(0), cur_stream()));
+  LAUNCH_OK(b200::sink_softmax_launch(s.data_ptr<float>(), sink.has_value() ? sink->data_ptr<float>() : nullptr, (int)H, (int)s.size(1), (int)ctx0,
+                                      (float)scale, out.data_ptr(), out_f32, (long long)s.size(0), (int)window, (int)k0, cur_stream()));
+  return out;
+}
+
+// x += (y + extra * sigmoid(gate)) * ls on the fp32 residual stream (in place); returns rms(x) * w in the activation type
+Tensor hy_scaled_add_norm_(Tensor x, const Tensor& y, const c10::optional<Tensor>& ls, const Tensor& w, double eps, bool act_f32,
+                           const c10::optional<Tensor>& extra, const c10::optional<Tensor>& gate) {
+  check_f32c(x, "x"); check_f32c(w, "w"); check_rows(y, "y");
+  TORCH_CHECK(y.is_cuda() && y.scalar_type() == torch::kFloat32 && x.dim() == 2 && y.size(0) == x.size(0) && y.size(1) == x.size(1) && w.numel() == x.size(1));
+  const float* lsp = nullptr; const float* ep = nullptr; const float* gp = nullptr; long long lde = 0, ldg = 0;
+  if (ls.has_value()) { check_f32c(*ls, "ls"); TORCH_CHECK(ls->numel() == x.size(1)); lsp = ls->data_ptr<float>(); }
+  if (extra.has_value()) {
+    TORCH_CHECK(gate.has_value() && extra->is_cuda() && extra->scalar_type() == torch::kFloat32 && gate->scalar_type() == torch::kFloat32 && gate->is_cuda());
+    check_rows(*extra, "extra");
+    TORCH_CHECK(extra->size(0) == x.size(0) && extra->size(1) == x.size(1) && gate->dim() == 1 && gate->size(0) == x.size(0));
+    ep = extra->data_ptr<float>(); lde = extra->stride(0); gp = gate->data_ptr<float>(); ldg = gate->stride(0);
+  }
+  const c10::cuda::CUDAGuard guard(x.device());
+  Tensor xa = torch::empty({x.size(0), x.size(1)}, x.options().dtype(act_type(act_f32)));
+  if (x.size(0) == 0) return xa;
+  LAUNCH_OK(b200::scaled_add_norm_launch(x.data_ptr<float>(), y.data_ptr<float>(), y.stride(0), lsp, ep, lde, gp, ldg, w.data_ptr<float>(), xa.data_ptr(),
+                                         act_f32, (int)x.size(1), (float)eps, (int)x.size(0), cur_stream()));
+  return xa;
+}
+
+Tensor hy_mlstm_scan(const Tensor& qkv, const Tensor& gates, const Tensor& gate_bias, Tensor S, Tensor n, Tensor m, const Tensor& cu, const Tensor& ctx,
+                     const Tensor& slots, int64_t H, int64_t Dk, int64_t V, int64_t PB, double cap, double q_scale, int64_t max_q) {
+  check_act(qkv, "qkv"); check_rows(qkv, "qkv"); check_rows(gates, "gates"); check_f32c(gate_bias, "gate_bias"); check_f32c(S, "S"); check_f32c(n, "n");
+  check_f32c(m, "m"); check_i32(cu, "cu_seqlens"); check_i32(ctx, "context_lens"); check_i32(slots, "state_slots");
+  TORCH_CHECK(gates.is_cuda() && gates.scalar_type() == torch::kFloat32 && gates.size(0) == qkv.size(0) && gates.size(1) >= 2 * H && gate_bias.numel() == 2 * H);
+  TORCH_CHECK(qkv.size(1) >= 2 * H * Dk + H * V && PB >= 1 && V % PB == 0 && PB <= 1024 && cap > 0);
+  const int64_t NB = V / PB;
+  TORCH_CHECK(S.dim() == 4 && S.size(1) == H && S.size(2) == Dk && S.size(3) == V && n.dim() == 4 && n.size(0) == S.size(0) && n.size(1) == H &&
+              n.size(2) == NB && n.size(3) == Dk && m.dim() == 3 && m.size(0) == S.size(0) && m.size(1) == H && m.size(2) == NB,
+              "mLSTM state: S [slots, H, dim, vdim], n [slots, H, vdim / col_block, dim], m [slots, H, vdim / col_block]");
+  const c10::cuda::CUDAGuard guard(qkv.device());
+  Tensor out = torch::empty({qkv.size(0), H * V}, qkv.options().dtype(torch::kFloat32));
+  if (qkv.size(0) == 0) return out;
+  LAUNCH_OK(b200::mlstm_scan_launch(qkv.data_ptr(), qkv.stride(0), gates.data_ptr<float>(), gates.stride(0), gate_bias.data_ptr<float>(), S.data_ptr<float>(),
+                                    n.data_ptr<float>(), m.data_ptr<float>(), cu.data_ptr<int>(), ctx.data_ptr<int>(), slots.data_ptr<int>(),
+                                    out.data_ptr<float>(), (int)slots.numel(), (int)H, (int)Dk, (int)V, (int)PB, (float)cap, (float)q_scale, is_f32(qkv),
+                                    (int)max_q, cur_stream()));
+  return out;
+}
+
+std::vector<Tensor> hy_sigmoid_topk(const Tensor& z, int64_t E, int64_t top) {
+  check_rows(z, "z");
+  TORCH_CHECK(z.is_cuda() && z.scalar_type() == torch::kFloat32 && z.dim() == 2 && z.size(1) >= E && top >= 1 && top <= E);
+  const c10::cuda::CUDAGuard guard(z.device());
+  Tensor idx = torch::empty({z.size(0), top}, z.options().dtype(torch::kInt32)), w = torch::empty({z.size(0), top}, z.options());
+  if (z.size(0) == 0) return {idx, w};
+  LAUNCH_OK(b200::sigmoid_topk_launch(z.data_ptr<float>(), z.stride(0), (int)E, (int)top, idx.data_ptr<int>(), w.data_ptr<float>(), (int)z.size(0), cur_stream()));
+  return {idx, w};
+}
+
+// row_of / scale (both optional, one entry per processed row): block i handles row row_of[i] of gu with scale[i]
+Tensor hy_clamped_glu(const Tensor& gu, double limit, const c10::optional<Tensor>& row_of, const c10::optional<Tensor>& scale) {
+  check_act(gu, "gu"); check_rows(gu, "gu");
+  TORCH_CHECK(gu.dim() == 2 && gu.size(1) % 2 == 0);
+  const int64_t F = gu.size(1) / 2, rows = row_of.has_value() ? row_of->numel() : gu.size(0);
+  if (row_of.has_value()) check_i32(*row_of, "row_of");
+  if (scale.has_value()) { check_f32c(*scale, "scale"); TORCH_CHECK(scale->numel() == rows); }
+  const c10::cuda::CUDAGuard guard(gu.device());
+  Tensor out = torch::empty({gu.size(0), F}, gu.options());
+  if (rows == 0) return out;
+  LAUNCH_OK(b200::clamped_glu_launch(gu.data_ptr(), gu.stride(0), (int)F, (float)limit, row_of.has_value() ? row_of->data_ptr<int>() : nullptr,
+                                     scale.has_value() ? scale->data_ptr<float>() : nullptr, out.data_ptr(), is_f32(gu), (int)rows, cur_stream()));
+  return out;
+}
+
+Tensor hy_gather_sum(const Tensor& y, const Tensor& row_of, int64_t k) {
+  check_f32c(y, "y"); check_i32(row_of, "row_of");
+  TORCH_CHECK(y.dim() == 2 && k >= 1 && row_of.numel() % k == 0);
+  const c10::cuda::CUDAGuard guard(y.device());
+  const int64_t T = row_of.numel() / k;
+  Tensor out = torch::empty({T, y.size(1)}, y.options());
+  if (T == 0) return out;
+  LAUNCH_OK(b200::gather_sum_launch(y.data_ptr<float>(), row_of.data_ptr<int>(), (int)k, (int)y.size(1), out.data_ptr<float>(), (int)T, cur_stream()));
   return out;
 }
 
@@ -1058,10 +1144,19 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hy_causal_conv_silu", &hy_causal_conv_silu);
   m.def("hy_ssm_scan", &hy_ssm_scan);
   m.def("hy_decay_scan", &hy_decay_scan);
-  m.def("hy_latent_prologue", &hy_latent_prologue);
-  m.def("hy_latent_attention", &hy_latent_attention);
-  m.def("hy_rotate_half_", &hy_rotate_half_);
-  m.def("hy_sink_softmax", &hy_sink_softmax);
+  m.def("hy_latent_prologue", &hy_latent_prologue, py::arg("x"), py::arg("q_rank"), py::arg("kv_rank"), py::arg("qn_w"), py::arg("kvn_w"), py::arg("eps"),
+        py::arg("pool"), py::arg("slot_map"), py::arg("positions"), py::arg("inv_freq"), py::arg("interleaved") = false);
+  m.def("hy_latent_attention", &hy_latent_attention, py::arg("q"), py::arg("pool"), py::arg("sink"), py::arg("block_tables"), py::arg("positions"),
+        py::arg("cu"), py::arg("scale"), py::arg("kv_rank"), py::arg("inv_freq"), py::arg("max_ctx"), py::arg("window") = 0, py::arg("interleaved") = false);
+  m.def("hy_rotate_half_", &hy_rotate_half_, py::arg("q"), py::arg("positions"), py::arg("inv_freq"), py::arg("kv_rank"), py::arg("interleaved") = false);
+  m.def("hy_sink_softmax", &hy_sink_softmax, py::arg("s"), py::arg("sink"), py::arg("H"), py::arg("ctx0"), py::arg("scale"), py::arg("out_f32"),
+        py::arg("window") = 0, py::arg("k0") = 0);
+  m.def("hy_scaled_add_norm_", &hy_scaled_add_norm_, py::arg("x"), py::arg("y"), py::arg("ls"), py::arg("w"), py::arg("eps"), py::arg("act_f32"),
+        py::arg("extra") = py::none(), py::arg("gate") = py::none());
+  m.def("hy_mlstm_scan", &hy_mlstm_scan);
+  m.def("hy_sigmoid_topk", &hy_sigmoid_topk);
+  m.def("hy_clamped_glu", &hy_clamped_glu, py::arg("gu"), py::arg("limit"), py::arg("row_of") = py::none(), py::arg("scale") = py::none());
+  m.def("hy_gather_sum", &hy_gather_sum);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });
   m.def("sm_arch", []() { return std::string("sm_100a"); });
 }

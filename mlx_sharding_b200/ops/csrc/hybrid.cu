@@ -288,18 +288,21 @@ __global__ void recurrent_scan_kernel(ScanArgs a, int PB, int kScanTokens) {
 }
 
 // ---------------------------------------------------------------------------------------------------------- latent attention
-// row [c_q raw: Qr | c raw: L | k_rot raw: R]  ->  cq = rms(c_q) * qn_w ;  pool[slot] = [rms(c) * kvn_w | rotate_half(k_rot, pos)]
+// row [c_q raw: Qr | c raw: L | k_rot raw: R]  ->  cq = rms(c_q) * qn_w ;  pool[slot] = [rms(c) * kvn_w | rotate(k_rot, pos)]
 template <typename AT>
 __global__ void latent_prologue_kernel(const AT* __restrict__ x, long long ld_x, int Qr, int L, int R, const float* __restrict__ qn_w,
                                        const float* __restrict__ kvn_w, float eps, AT* __restrict__ cq, AT* __restrict__ pool,
-                                       const int* __restrict__ slot_map, const int* __restrict__ positions, const float* __restrict__ inv_freq) {
+                                       const int* __restrict__ slot_map, const int* __restrict__ positions, const float* __restrict__ inv_freq,
+                                       int interleaved) {
   __shared__ float red[32];
   const long long t = blockIdx.x;
   const AT* row = x + t * ld_x;
-  float ss = 0.f;
-  for (int c = threadIdx.x; c < Qr; c += blockDim.x) { const float v = ldf<AT>(row + c); ss += v * v; }
-  float r = rsqrtf(block_sum(ss, red) / (float)Qr + eps);
-  for (int c = threadIdx.x; c < Qr; c += blockDim.x) stf<AT>(cq + t * Qr + c, ldf<AT>(row + c) * r * qn_w[c]);
+  float ss = 0.f, r;
+  if (Qr > 0) {     // Qr == 0: a design without a query latent
+    for (int c = threadIdx.x; c < Qr; c += blockDim.x) { const float v = ldf<AT>(row + c); ss += v * v; }
+    r = rsqrtf(block_sum(ss, red) / (float)Qr + eps);
+    for (int c = threadIdx.x; c < Qr; c += blockDim.x) stf<AT>(cq + t * Qr + c, ldf<AT>(row + c) * r * qn_w[c]);
+  }
   ss = 0.f;
   for (int c = threadIdx.x; c < L; c += blockDim.x) { const float v = ldf<AT>(row + Qr + c); ss += v * v; }
   r = rsqrtf(block_sum(ss, red) / (float)L + eps);
@@ -310,9 +313,10 @@ __global__ void latent_prologue_kernel(const AT* __restrict__ x, long long ld_x,
   for (int i = threadIdx.x; i < half; i += blockDim.x) {
     float sn, cs;
     sincosf(pos * inv_freq[i], &sn, &cs);
-    const float u = ldf<AT>(row + Qr + L + i), v = ldf<AT>(row + Qr + L + half + i);
-    stf<AT>(dst + L + i, u * cs - v * sn);
-    stf<AT>(dst + L + half + i, v * cs + u * sn);
+    const int iu = interleaved ? 2 * i : i, iv = interleaved ? 2 * i + 1 : half + i;     // pair (2i, 2i+1) or (i, i + R/2)
+    const float u = ldf<AT>(row + Qr + L + iu), v = ldf<AT>(row + Qr + L + iv);
+    stf<AT>(dst + L + iu, u * cs - v * sn);
+    stf<AT>(dst + L + iv, v * cs + u * sn);
   }
 }
 
@@ -328,7 +332,7 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
                                         const int* __restrict__ block_tables, int max_blocks, const int* __restrict__ positions,
                                         const int* __restrict__ cu, int B, int H, int L, int R, int page, float scale,
                                         const float* __restrict__ inv_freq, AT* __restrict__ out, int nsplit, int chunk,
-                                        float* __restrict__ part) {
+                                        float* __restrict__ part, int window, int interleaved) {
   extern __shared__ float smem[];
   const int Dq = L + R, ldk = VEC ? Dq + 4 : Dq + 1, nw = blockDim.x >> 5;
   float* qs = smem;                       // [nw][Dq]
@@ -347,24 +351,29 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
       const AT* qr = q + ((long long)t * H + hh) * Dq;
       if (d < L) v = ldf<AT>(qr + d);
       else {
-        const int e = d - L, f = e < half ? e : e - half;
+        const int e = d - L, f = interleaved ? e >> 1 : (e < half ? e : e - half);
+        const bool first = interleaved ? (e & 1) == 0 : e < half;
         float sn, cs;
         sincosf((float)pos * inv_freq[f], &sn, &cs);
-        const float u = ldf<AT>(qr + L + f), w = ldf<AT>(qr + L + half + f);
-        v = rnd<AT>(e < half ? u * cs - w * sn : w * cs + u * sn);
+        const float u = ldf<AT>(qr + L + (interleaved ? 2 * f : f)), w = ldf<AT>(qr + L + (interleaved ? 2 * f + 1 : half + f));
+        v = rnd<AT>(first ? u * cs - w * sn : w * cs + u * sn);
       }
     }
     qs[i] = v;
   }
   // the sink: one extra term exp(sink - m) of the denominator, no key, no value (added by the combine kernel when keys are split)
-  float m = nsplit > 1 ? -INFINITY : (h < H ? sink[h] : 0.f), l = nsplit > 1 ? 0.f : 1.f;
+  // (sink == nullptr: the ordinary softmax.)  window > 0: only keys pos - window < j <= pos are visible; key splits count from the
+  // first visible key of this token
+  const bool has_sink = sink != nullptr && nsplit == 1;
+  float m = has_sink ? (h < H ? sink[h] : 0.f) : -INFINITY, l = has_sink ? 1.f : 0.f;
+  const int jlo = window > 0 ? max(0, pos - window + 1) : 0;
   float o[NPL];
 #pragma unroll
   for (int i = 0; i < NPL; ++i) o[i] = 0.f;
   const int nper = (L + 31) / 32;
   const float* qh = qs + warp * Dq;
-  const int jend = min(pos + 1, (int)(blockIdx.z + 1) * chunk);
-  for (int j0 = blockIdx.z * chunk; j0 < jend; j0 += kLatTile) {
+  const int jend = (int)min((long long)pos + 1, (long long)jlo + (long long)(blockIdx.z + 1) * chunk);
+  for (int j0 = jlo + blockIdx.z * chunk; j0 < jend; j0 += kLatTile) {
     __syncthreads();
     const int nk = min(kLatTile, jend - j0);
     // each warp fetches whole rows: 16-byte chunks per lane (several independent loads in flight), one block-table lookup per row
@@ -432,7 +441,7 @@ __global__ void latent_attention_kernel(const AT* __restrict__ q, const AT* __re
   }
   // register i of a lane holds output dim: VEC 4 lane + 128 (i / 4) + i % 4, else lane + 32 i
   if (h < H && nsplit == 1) {
-    const float inv = 1.f / l;
+    const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll
     for (int i = 0; i < NPL; ++i) {
       const int d = VEC ? 4 * lane + 128 * (i / 4) + (i % 4) : lane + 32 * i;
@@ -455,10 +464,10 @@ __global__ void latent_combine_kernel(const float* __restrict__ part, const floa
                                       AT* __restrict__ out) {
   const long long th = blockIdx.x;
   const float* pp = part + th * nsplit * (L + 2);
-  const float sk = sink[th % H];
+  const float sk = sink != nullptr ? sink[th % H] : -INFINITY;
   float M = sk;
   for (int z = 0; z < nsplit; ++z) M = fmaxf(M, pp[z * (L + 2)]);
-  float den = expf(sk - M);
+  float den = sink != nullptr ? expf(sk - M) : 0.f;
   for (int z = 0; z < nsplit; ++z) { const float mz = pp[z * (L + 2)]; if (mz != -INFINITY) den += pp[z * (L + 2) + 1] * expf(mz - M); }
   for (int d = threadIdx.x; d < L; d += blockDim.x) {
     float acc = 0.f;
@@ -472,7 +481,7 @@ __global__ void latent_combine_kernel(const float* __restrict__ part, const floa
 // rotate-half rotary, in place, on dims [L, L + R) of every head of q [T, H, L + R]
 template <typename AT>
 __global__ void rotate_half_kernel(AT* __restrict__ q, const int* __restrict__ positions, const float* __restrict__ inv_freq, int H, int L,
-                                   int R) {
+                                   int R, int interleaved) {
   const int t = blockIdx.x, half = R / 2;
   const float pos = (float)positions[t];
   for (int i = threadIdx.x; i < H * half; i += blockDim.x) {
@@ -480,32 +489,224 @@ __global__ void rotate_half_kernel(AT* __restrict__ q, const int* __restrict__ p
     AT* p = q + ((long long)t * H + h) * (L + R) + L;
     float sn, cs;
     sincosf(pos * inv_freq[f], &sn, &cs);
-    const float u = ldf<AT>(p + f), v = ldf<AT>(p + half + f);
-    stf<AT>(p + f, u * cs - v * sn);
-    stf<AT>(p + half + f, v * cs + u * sn);
+    const int iu = interleaved ? 2 * f : f, iv = interleaved ? 2 * f + 1 : half + f;
+    const float u = ldf<AT>(p + iu), v = ldf<AT>(p + iv);
+    stf<AT>(p + iu, u * cs - v * sn);
+    stf<AT>(p + iv, v * cs + u * sn);
   }
 }
 
-// row r = (token t, head h) of raw scores [rows, n]; keys j <= ctx0 + t are visible; p_j = e^(s_j scale - m) / (e^(sink_h - m) + sum)
+// row r = (token t, head h) of raw scores [rows, n]; column j is the key at position k0 + j; the query sits at position ctx0 + t and sees
+// keys at positions <= its own (and > its own - window when window > 0); p_j = e^(s_j scale - m) / (e^(sink_h - m) + sum), the sink
+// term only when sink != nullptr
 template <typename AT>
 __global__ void sink_softmax_kernel(const float* __restrict__ s, const float* __restrict__ sink, int H, int n, int ctx0, float scale,
-                                    AT* __restrict__ out) {
+                                    AT* __restrict__ out, int window, int k0) {
   __shared__ float red[32];
   const long long r = blockIdx.x;
-  const int t = (int)(r / H), h = (int)(r % H), nv = min(n, ctx0 + t + 1);
+  const int t = (int)(r / H), h = (int)(r % H), qp = ctx0 + t;
+  const int nv = max(0, min(n, qp - k0 + 1)), j_lo = window > 0 ? max(0, qp - window + 1 - k0) : 0;
   const float* row = s + r * n;
-  const float sk = sink[h];
+  const float sk = sink != nullptr ? sink[h] : -INFINITY;
   float m = sk;
-  for (int j = threadIdx.x; j < nv; j += blockDim.x) m = fmaxf(m, row[j] * scale);
+  for (int j = j_lo + threadIdx.x; j < nv; j += blockDim.x) m = fmaxf(m, row[j] * scale);
   m = warp_max(m);
   const int w = threadIdx.x >> 5, l = threadIdx.x & 31, nw = blockDim.x >> 5;
   if (l == 0) red[w] = m;
   __syncthreads();
   m = warp_max(l < nw ? red[l] : -INFINITY);
   float sum = 0.f;
-  for (int j = threadIdx.x; j < nv; j += blockDim.x) sum += expf(row[j] * scale - m);
-  const float inv = 1.f / (block_sum(sum, red) + expf(sk - m));
-  for (int j = threadIdx.x; j < n; j += blockDim.x) stf<AT>(out + r * n + j, j < nv ? expf(row[j] * scale - m) * inv : 0.f);
+  for (int j = j_lo + threadIdx.x; j < nv; j += blockDim.x) sum += expf(row[j] * scale - m);
+  const float inv = 1.f / (block_sum(sum, red) + (sink != nullptr ? expf(sk - m) : 0.f));
+  for (int j = threadIdx.x; j < n; j += blockDim.x) stf<AT>(out + r * n + j, (j >= j_lo && j < nv) ? expf(row[j] * scale - m) * inv : 0.f);
+}
+
+// ---------------------------------------------------------------------------------------------------------- pre-norm residual step
+// x += (y + extra * sigmoid(gate[t])) * ls   (x, y, extra fp32; ls, extra nullable);   xa = (AT)(x * rsqrt(mean(x^2) + eps) * w)
+template <typename AT>
+__global__ void scaled_add_norm_kernel(float* __restrict__ x, const float* __restrict__ y, long long ld_y, const float* __restrict__ ls,
+                                       const float* __restrict__ extra, long long ld_e, const float* __restrict__ gate, long long ld_gate,
+                                       const float* __restrict__ w, AT* __restrict__ xa, int n, float eps) {
+  __shared__ float red[32];
+  const long long t = blockIdx.x;
+  const float* yr = y + t * ld_y;
+  const float* er = extra != nullptr ? extra + t * ld_e : nullptr;
+  const float sg = extra != nullptr ? sigmoid_f(gate[t * ld_gate]) : 0.f;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < n; c += blockDim.x) {
+    float v = yr[c];
+    if (er != nullptr) v += er[c] * sg;
+    if (ls != nullptr) v *= ls[c];
+    v += x[t * n + c];
+    x[t * n + c] = v;
+    ss += v * v;
+  }
+  const float r = rsqrtf(block_sum(ss, red) / (float)n + eps);
+  for (int c = threadIdx.x; c < n; c += blockDim.x) stf<AT>(xa + t * n + c, x[t * n + c] * r * w[c]);   // own writes: same thread, same c
+}
+
+// ---------------------------------------------------------------------------------------------------------- mLSTM scan
+// Matrix memory with exponential gating, stabilised by a running maximum m (all fp32):
+//   i = cap tanh((gi + bi) / cap), f = logsigmoid(cap tanh((gf + bf) / cap)), m' = max(f + m, i), a = e^(f + m - m'), b = e^(i - m')
+//   S <- a S + b k v^T,  n <- a n + b k,  o = S^T q / (max(|n . q|, e^(-m')) + 1e-6);   S, n, m start at zero.
+// One CTA per (sequence, head, block of PB value columns); S[N][PB] and n[N] in shared memory.  The normaliser n and the maximum m do
+// not depend on the value column, so every column block keeps its OWN copy of them in the state (no CTA reads what another writes).
+struct MlstmArgs {
+  const void* in; long long ld_in;        // [q: H*N | k: H*N | v: H*P | ...] activations
+  const float* gates; long long ld_g;     // raw [gi: H | gf: H] fp32
+  const float* gate_bias;                 // [2H]
+  float* S; float* n; float* m;           // [slots, H, N, P], [slots, H, P/PB, N], [slots, H, P/PB]
+  const int* cu; const int* ctx; const int* slots;
+  float* out;                             // fp32 [T, H * P]
+  int H, N, P;
+  float cap, q_scale;
+};
+
+__device__ __forceinline__ float logsigmoid_f(float v) { return fminf(v, 0.f) - log1pf(expf(-fabsf(v))); }
+
+template <typename AT>
+__global__ void mlstm_scan_kernel(MlstmArgs a, int PB, int R, int kTok) {
+  extern __shared__ float smem[];
+  const int b = blockIdx.x, h = blockIdx.y, N = a.N, P = a.P, H = a.H, NB = P / PB, p0 = blockIdx.z * PB;
+  const int p = threadIdx.x % PB, r = threadIdx.x / PB, warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+  float* S = smem;                          // [N][PB]
+  float* nv = S + N * PB;                   // [N]
+  float* red = nv + N;                      // [2][R][PB]
+  float* redn = red + 2 * R * PB;           // [2][32]
+  float* kq = redn + 64;                    // [tokens][2N]   b k | q_scale q
+  float* xs = kq + kTok * 2 * N;            // [tokens][PB]
+  float* da = xs + kTok * PB;               // [tokens] a        (log first, then the exponential)
+  float* db = da + kTok;                    // [tokens] b
+  float* dm = db + kTok;                    // [tokens] e^(-m')
+  float* gi = dm + kTok;                    // [tokens]
+  float* gf = gi + kTok;                    // [tokens]
+  float* mrun = gf + kTok;                  // [1]
+  const int s = a.cu[b], q = a.cu[b + 1] - s;
+  if (q == 0) return;
+  const bool fresh = a.ctx[b] - q == 0;
+  const long long sh = (long long)a.slots[b] * H + h;
+  float* gS = a.S + sh * N * P;
+  float* gn = a.n + (sh * NB + blockIdx.z) * N;
+  float* gm = a.m + sh * NB + blockIdx.z;
+  for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; S[e] = fresh ? 0.f : gS[n * P + p0 + c]; }
+  for (int e = threadIdx.x; e < N; e += blockDim.x) nv[e] = fresh ? 0.f : gn[e];
+  if (threadIdx.x == 0) mrun[0] = fresh ? 0.f : gm[0];
+  const AT* in = reinterpret_cast<const AT*>(a.in);
+  const float bi = a.gate_bias[h], bf = a.gate_bias[H + h], cap = a.cap;
+  for (int j0 = 0; j0 < q; j0 += kTok) {
+    const int nt = min(kTok, q - j0);
+    __syncthreads();                        // the last block's operands are no longer read (and the state is loaded)
+    for (int jj = threadIdx.x; jj < nt; jj += blockDim.x) {
+      const float* g = a.gates + (long long)(s + j0 + jj) * a.ld_g;
+      gi[jj] = cap * tanhf((g[h] + bi) / cap);
+      gf[jj] = logsigmoid_f(cap * tanhf((g[H + h] + bf) / cap));
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {                 // the running maximum is a scalar chain: additions and maxima only
+      float m = mrun[0];
+      for (int jj = 0; jj < nt; ++jj) {
+        const float mn = fmaxf(gf[jj] + m, gi[jj]);
+        da[jj] = gf[jj] + m - mn; db[jj] = gi[jj] - mn; dm[jj] = -mn;
+        m = mn;
+      }
+      mrun[0] = m;
+    }
+    __syncthreads();
+    for (int jj = threadIdx.x; jj < nt; jj += blockDim.x) { da[jj] = expf(da[jj]); db[jj] = expf(db[jj]); dm[jj] = expf(dm[jj]); }
+    __syncthreads();
+    for (int e = threadIdx.x; e < 2 * N + PB; e += blockDim.x) {
+      const int col = e < N ? H * N + h * N + e : (e < 2 * N ? h * N + (e - N) : 2 * H * N + h * P + p0 + (e - 2 * N));
+      const AT* src = in + (long long)(s + j0) * a.ld_in + col;
+#pragma unroll 4
+      for (int jj = 0; jj < nt; ++jj) {
+        float v = ldf<AT>(src + (long long)jj * a.ld_in);
+        if (e < N) v *= db[jj];
+        else if (e < 2 * N) v *= a.q_scale;
+        if (e < 2 * N) kq[jj * 2 * N + e] = v;
+        else xs[jj * PB + e - 2 * N] = v;
+      }
+    }
+    __syncthreads();
+    for (int jj = 0; jj < nt; ++jj) {
+      const int j = j0 + jj;
+      const float decay = da[jj], xv = xs[jj * PB + p];
+      const float* kr = kq + jj * 2 * N;
+      if (r < R) {
+        float acc = 0.f;
+        for (int n = r; n < N; n += R) {
+          const float sv = decay * S[n * PB + p] + kr[n] * xv;
+          S[n * PB + p] = sv;
+          acc += sv * kr[N + n];
+        }
+        red[((j & 1) * R + r) * PB + p] = acc;
+      }
+      float pn = 0.f;                       // normaliser: element e of n belongs to thread e % blockDim
+      for (int e = threadIdx.x; e < N; e += blockDim.x) {
+        const float nn = decay * nv[e] + kr[e];
+        nv[e] = nn;
+        pn += nn * kr[N + e];
+      }
+      pn = warp_sum(pn);
+      if (lane == 0) redn[(j & 1) * 32 + warp] = pn;
+      __syncthreads();
+      if (r == 0) {
+        float y = 0.f, nq = 0.f;
+        for (int i = 0; i < R; ++i) y += red[((j & 1) * R + i) * PB + p];
+        for (int i = 0; i < nw; ++i) nq += redn[(j & 1) * 32 + i];
+        a.out[(long long)(s + j) * H * P + h * P + p0 + p] = y / (fmaxf(fabsf(nq), dm[jj]) + 1e-6f);
+      }
+    }
+  }
+  __syncthreads();
+  for (int e = threadIdx.x; e < N * PB; e += blockDim.x) { const int n = e / PB, c = e % PB; gS[n * P + p0 + c] = S[e]; }
+  for (int e = threadIdx.x; e < N; e += blockDim.x) gn[e] = nv[e];
+  if (threadIdx.x == 0) gm[0] = mrun[0];
+}
+
+// ---------------------------------------------------------------------------------------------------------- mixture of experts
+// Router on fp32 logits: scores sigmoid(z), the `top` largest (ties: lowest id), weights = the chosen scores.  One warp per token.
+__global__ void sigmoid_topk_kernel(const float* __restrict__ z, long long ld_z, int E, int top, int* __restrict__ idx, float* __restrict__ w) {
+  extern __shared__ float sc[];             // [E]
+  const long long t = blockIdx.x;
+  const int lane = threadIdx.x;
+  for (int e = lane; e < E; e += 32) sc[e] = sigmoid_f(z[t * ld_z + e]);
+  __syncwarp();
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY; int bi = 0x7fffffff;
+    for (int e = lane; e < E; e += 32) { const float v = sc[e]; if (v > best) { best = v; bi = e; } }   // ascending e: first maximum wins
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+      if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+    }
+    if (lane == 0) { idx[t * top + j] = bi; w[t * top + j] = best; sc[bi] = -INFINITY; }
+    __syncwarp();
+  }
+}
+
+// [g | u] rows (F each) -> g' sigmoid(1.702 g') (u' + 1),  g' = min(s g, limit), u' = clamp(s u, +-limit).  Block i handles row
+// row_of[i] with scale s = scale[i] (both nullable: row i, scale 1): scaling a projection's output equals scaling its input.
+template <typename AT>
+__global__ void clamped_glu_kernel(const AT* __restrict__ gu, long long ld, int F, float limit, const int* __restrict__ row_of,
+                                   const float* __restrict__ scale, AT* __restrict__ out) {
+  const long long r = row_of != nullptr ? row_of[blockIdx.x] : blockIdx.x;
+  const float s = scale != nullptr ? scale[blockIdx.x] : 1.f;
+  const AT* row = gu + r * ld;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < F; c += gridDim.y * blockDim.x) {
+    const float g = fminf(s * ldf<AT>(row + c), limit), u = fminf(fmaxf(s * ldf<AT>(row + F + c), -limit), limit);
+    stf<AT>(out + r * F + c, g * sigmoid_f(1.702f * g) * (u + 1.f));
+  }
+}
+
+// out[t] = sum_j y[row_of[t * k + j]]   (fp32): the routed experts' results back in token order
+__global__ void gather_sum_kernel(const float* __restrict__ y, const int* __restrict__ row_of, int k, int n, float* __restrict__ out) {
+  const long long t = blockIdx.x;
+  for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < n; c += gridDim.y * blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < k; ++j) acc += y[(long long)row_of[t * k + j] * n + c];
+    out[t * n + c] = acc;
+  }
 }
 
 inline cudaError_t last() { return cudaGetLastError(); }
@@ -607,26 +808,28 @@ cudaError_t decay_scan_launch(const void* qkv, long long ld, const float* decay,
 
 cudaError_t latent_prologue_launch(const void* x, long long ld_x, int Qr, int L, int R, const float* qn_w, const float* kvn_w, float eps,
                                    void* cq, void* pool, const int* slot_map, const int* positions, const float* inv_freq, bool f32, int T,
-                                   cudaStream_t s) {
+                                   int interleaved, cudaStream_t s) {
   AT_DISPATCH(f32, (latent_prologue_kernel<AT><<<T, 256, 0, s>>>((const AT*)x, ld_x, Qr, L, R, qn_w, kvn_w, eps, (AT*)cq, (AT*)pool, slot_map,
-                                                                 positions, inv_freq)));
+                                                                 positions, inv_freq, interleaved)));
   return last();
 }
 
-cudaError_t rotate_half_launch(void* q, const int* positions, const float* inv_freq, int H, int L, int R, bool f32, int T, cudaStream_t s) {
-  AT_DISPATCH(f32, (rotate_half_kernel<AT><<<T, 128, 0, s>>>((AT*)q, positions, inv_freq, H, L, R)));
+cudaError_t rotate_half_launch(void* q, const int* positions, const float* inv_freq, int H, int L, int R, bool f32, int T, int interleaved,
+                               cudaStream_t s) {
+  AT_DISPATCH(f32, (rotate_half_kernel<AT><<<T, 128, 0, s>>>((AT*)q, positions, inv_freq, H, L, R, interleaved)));
   return last();
 }
 
 cudaError_t sink_softmax_launch(const float* sc, const float* sink, int H, int n, int ctx0, float scale, void* out, bool f32, long long rows,
-                                cudaStream_t s) {
-  AT_DISPATCH(f32, (sink_softmax_kernel<AT><<<(unsigned)rows, 256, 0, s>>>(sc, sink, H, n, ctx0, scale, (AT*)out)));
+                                int window, int k0, cudaStream_t s) {
+  AT_DISPATCH(f32, (sink_softmax_kernel<AT><<<(unsigned)rows, 256, 0, s>>>(sc, sink, H, n, ctx0, scale, (AT*)out, window, k0)));
   return last();
 }
 
 cudaError_t latent_attention_launch(const void* q, const void* pool, const float* sink, const int* block_tables, int max_blocks,
                                     const int* positions, const int* cu, int B, int H, int L, int R, int page, float scale,
-                                    const float* inv_freq, void* out, bool f32, int T, int nsplit, int chunk, float* part, cudaStream_t s) {
+                                    const float* inv_freq, void* out, bool f32, int T, int nsplit, int chunk, float* part, int window,
+                                    int interleaved, cudaStream_t s) {
   if (L > 32 * kLatMaxPerLane || nsplit < 1 || (nsplit > 1 && part == nullptr)) return cudaErrorInvalidValue;
   const int nw = H < 8 ? H : 8, Dq = L + R;
   const bool vec = L % 128 == 0 && Dq % 4 == 0;
@@ -640,12 +843,62 @@ cudaError_t latent_attention_launch(const void* q, const void* pool, const float
       if (e != cudaSuccess) return e;                                                                                                  \
     }                                                                                                                                  \
     k<<<grid, nw * 32, smem, s>>>((const AT_*)q, (const AT_*)pool, sink, block_tables, max_blocks, positions, cu, B, H, L, R, page, scale, \
-                                  inv_freq, (AT_*)out, nsplit, chunk, part);                                                           \
+                                  inv_freq, (AT_*)out, nsplit, chunk, part, window, interleaved);                                      \
     if (nsplit > 1) latent_combine_kernel<AT_><<<T * H, 128, 0, s>>>(part, sink, H, L, nsplit, (AT_*)out);                             \
   } while (0)
   if (f32) { if (vec) LAT_LAUNCH(float, true); else LAT_LAUNCH(float, false); }
   else { if (vec) LAT_LAUNCH(__nv_bfloat16, true); else LAT_LAUNCH(__nv_bfloat16, false); }
 #undef LAT_LAUNCH
+  return last();
+}
+
+cudaError_t scaled_add_norm_launch(float* x, const float* y, long long ld_y, const float* ls, const float* extra, long long ld_e,
+                                   const float* gate, long long ld_gate, const float* w, void* xa, bool f32, int n, float eps, int T,
+                                   cudaStream_t s) {
+  AT_DISPATCH(f32, (scaled_add_norm_kernel<AT><<<T, 256, 0, s>>>(x, y, ld_y, ls, extra, ld_e, gate, ld_gate, w, (AT*)xa, n, eps)));
+  return last();
+}
+
+cudaError_t mlstm_scan_launch(const void* in, long long ld_in, const float* gates, long long ld_g, const float* gate_bias, float* S, float* n,
+                              float* m, const int* cu, const int* ctx, const int* slots, float* out, int B, int H, int N, int P, int PB,
+                              float cap, float q_scale, bool f32, int max_q, cudaStream_t s) {
+  if (PB < 1 || P % PB != 0 || PB > 1024) return cudaErrorInvalidValue;
+  MlstmArgs a{in, ld_in, gates, ld_g, gate_bias, S, n, m, cu, ctx, slots, out, H, N, P, cap, q_scale};
+  int R = 256 / PB;
+  if (R < 1) R = 1;
+  if (R > N) R = N;
+  const int threads = (R * PB + 31) / 32 * 32;   // tail threads (r >= R) help with staging, the normaliser and the state copy
+  const int stage = max_q < 1 ? 1 : (max_q < kScanTokensMax ? max_q : kScanTokensMax);
+  const size_t smem = ((size_t)N * PB + N + 2 * (size_t)R * PB + 64 + (size_t)stage * (2 * N + PB + 5) + 1) * sizeof(float);
+  if (smem > 220 * 1024) return cudaErrorInvalidValue;
+  if (f32) {
+    auto k = mlstm_scan_kernel<float>;
+    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+    k<<<dim3(B, H, P / PB), threads, smem, s>>>(a, PB, R, stage);
+  } else {
+    auto k = mlstm_scan_kernel<__nv_bfloat16>;
+    if (smem > 48 * 1024) { cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); if (e != cudaSuccess) return e; }
+    k<<<dim3(B, H, P / PB), threads, smem, s>>>(a, PB, R, stage);
+  }
+  return last();
+}
+
+cudaError_t sigmoid_topk_launch(const float* z, long long ld_z, int E, int top, int* idx, float* w, int T, cudaStream_t s) {
+  if (top > E || (size_t)E * sizeof(float) > 48 * 1024) return cudaErrorInvalidValue;
+  sigmoid_topk_kernel<<<T, 32, E * sizeof(float), s>>>(z, ld_z, E, top, idx, w);
+  return last();
+}
+
+cudaError_t clamped_glu_launch(const void* gu, long long ld, int F, float limit, const int* row_of, const float* scale, void* out, bool f32,
+                               int rows, cudaStream_t s) {
+  dim3 grid(rows, (F + 1023) / 1024);
+  AT_DISPATCH(f32, (clamped_glu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)gu, ld, F, limit, row_of, scale, (AT*)out)));
+  return last();
+}
+
+cudaError_t gather_sum_launch(const float* y, const int* row_of, int k, int n, float* out, int T, cudaStream_t s) {
+  dim3 grid(T, (n + 1023) / 1024);
+  gather_sum_kernel<<<grid, 256, 0, s>>>(y, row_of, k, n, out);
   return last();
 }
 
