@@ -635,6 +635,14 @@ def moe_clamped_experts(x, idx, w, Wgu: LinearWeight, Wd: LinearWeight, limit: f
         h = c.hy_clamped_glu(gu, float(limit), pair_row, w.reshape(-1))
         y = c.grouped_linear(h, wd, None, offs, T, 0, True)
         return c.hy_gather_sum(y, pair_row, int(k))
+    R = T * k
+    if R <= PAIR_KERNEL_MAX_ROWS or torch.cuda.is_current_stream_capturing():
+        # few rows (decode steps; anything inside a graph capture): every (token, choice) pair reads its expert's rows itself
+        ids = idx.reshape(-1).contiguous()
+        gu = c.hy_expert_rows_linear(x, int(k), wgu, ids, False)
+        h = c.hy_clamped_glu(gu, float(limit), None, w.reshape(-1).contiguous())
+        y = c.hy_expert_rows_linear(h, 1, wd, ids, True)
+        return y if k == 1 else y.view(T, k, K).sum(1)
     flat = idx.reshape(-1).long()
     order = torch.sort(flat, stable=True).indices
     pair_row = torch.empty_like(order, dtype=torch.int32)
@@ -655,3 +663,6 @@ def moe_clamped_experts(x, idx, w, Wgu: LinearWeight, Wd: LinearWeight, limit: f
             y[r0:r0 + n] = torch.matmul(h[r0:r0 + n], wd[e].t()).float()
         r0 += n
     return c.hy_gather_sum(y, pair_row, int(k))
+
+
+PAIR_KERNEL_MAX_ROWS = 64

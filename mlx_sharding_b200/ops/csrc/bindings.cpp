@@ -1052,6 +1052,21 @@ Tensor hy_clamped_glu(const Tensor& gu, double limit, const c10::optional<Tensor
   return out;
 }
 
+// out[i] = W[expert[i]] x[i / div]   (W [E, N, K]; fp32 accumulate; out fp32 when out_f32 or in exact mode)
+Tensor hy_expert_rows_linear(const Tensor& x, int64_t div, const Tensor& W, const Tensor& expert, bool out_f32) {
+  check_act(x, "x"); check_rows(x, "x"); check_i32(expert, "expert");
+  TORCH_CHECK(W.is_cuda() && W.is_contiguous() && W.dim() == 3 && W.scalar_type() == x.scalar_type() && W.size(2) == x.size(1) && div >= 1 &&
+              expert.numel() <= x.size(0) * div);
+  const c10::cuda::CUDAGuard guard(x.device());
+  const int64_t rows = expert.numel(), N = W.size(1);
+  const bool f32 = is_f32(x);
+  Tensor out = torch::empty({rows, N}, x.options().dtype(act_type(f32 || out_f32)));
+  if (rows == 0) return out;
+  LAUNCH_OK(b200::expert_rows_linear_launch(x.data_ptr(), x.stride(0), (int)div, W.data_ptr(), expert.data_ptr<int>(), (int)N, (int)W.size(2), out.data_ptr(),
+                                            f32, out_f32, (int)rows, cur_stream()));
+  return out;
+}
+
 Tensor hy_gather_sum(const Tensor& y, const Tensor& row_of, int64_t k) {
   check_f32c(y, "y"); check_i32(row_of, "row_of");
   TORCH_CHECK(y.dim() == 2 && k >= 1 && row_of.numel() % k == 0);
@@ -1157,6 +1172,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("hy_sigmoid_topk", &hy_sigmoid_topk);
   m.def("hy_clamped_glu", &hy_clamped_glu, py::arg("gu"), py::arg("limit"), py::arg("row_of") = py::none(), py::arg("scale") = py::none());
   m.def("hy_gather_sum", &hy_gather_sum);
+  m.def("hy_expert_rows_linear", &hy_expert_rows_linear);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });
   m.def("sm_arch", []() { return std::string("sm_100a"); });
 }

@@ -699,6 +699,23 @@ __global__ void clamped_glu_kernel(const AT* __restrict__ gu, long long ld, int 
   }
 }
 
+// out[i, n] = sum_k x[src(i), k] * W[expert[i], n, k]  (fp32 accumulate): one weight bank row per warp, every row with its own expert.
+// src(i) = i / div (div = top-k when x holds one row per token and i counts (token, choice) pairs).  Exact-mode and odd-size path of
+// the routed experts; no host involvement, so it can sit in a captured graph.        grid (rows, ceil(N / warps))
+template <typename AT, typename OT>
+__global__ void expert_rows_linear_kernel(const AT* __restrict__ x, long long ld_x, int div, const AT* __restrict__ W, const int* __restrict__ expert,
+                                          int N, int K, OT* __restrict__ out) {
+  const long long i = blockIdx.x;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, n = blockIdx.y * (blockDim.x >> 5) + warp;
+  if (n >= N) return;
+  const AT* xr = x + (i / div) * ld_x;
+  const AT* wr = W + ((long long)expert[i] * N + n) * K;
+  float acc = 0.f;
+  for (int k = lane; k < K; k += 32) acc += ldf<AT>(xr + k) * ldf<AT>(wr + k);
+  acc = warp_sum(acc);
+  if (lane == 0) stf<OT>(out + i * N + n, acc);
+}
+
 // out[t] = sum_j y[row_of[t * k + j]]   (fp32): the routed experts' results back in token order
 __global__ void gather_sum_kernel(const float* __restrict__ y, const int* __restrict__ row_of, int k, int n, float* __restrict__ out) {
   const long long t = blockIdx.x;
@@ -893,6 +910,15 @@ cudaError_t clamped_glu_launch(const void* gu, long long ld, int F, float limit,
                                int rows, cudaStream_t s) {
   dim3 grid(rows, (F + 1023) / 1024);
   AT_DISPATCH(f32, (clamped_glu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)gu, ld, F, limit, row_of, scale, (AT*)out)));
+  return last();
+}
+
+cudaError_t expert_rows_linear_launch(const void* x, long long ld_x, int div, const void* W, const int* expert, int N, int K, void* out, bool f32,
+                                      bool out_f32, int rows, cudaStream_t s) {
+  dim3 grid(rows, (N + 7) / 8);
+  if (f32) expert_rows_linear_kernel<float, float><<<grid, 256, 0, s>>>((const float*)x, ld_x, div, (const float*)W, expert, N, K, (float*)out);
+  else if (out_f32) expert_rows_linear_kernel<__nv_bfloat16, float><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, div, (const __nv_bfloat16*)W, expert, N, K, (float*)out);
+  else expert_rows_linear_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, s>>>((const __nv_bfloat16*)x, ld_x, div, (const __nv_bfloat16*)W, expert, N, K, (__nv_bfloat16*)out);
   return last();
 }
 

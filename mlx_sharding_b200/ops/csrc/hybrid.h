@@ -42,5 +42,7 @@ cudaError_t mlstm_scan_launch(const void* in, long long ld_in, const float* gate
 cudaError_t sigmoid_topk_launch(const float* z, long long ld_z, int E, int top, int* idx, float* w, int T, cudaStream_t s);
 cudaError_t clamped_glu_launch(const void* gu, long long ld, int F, float limit, const int* row_of, const float* scale, void* out, bool f32,
                                int rows, cudaStream_t s);
+cudaError_t expert_rows_linear_launch(const void* x, long long ld_x, int div, const void* W, const int* expert, int N, int K, void* out, bool f32,
+                                      bool out_f32, int rows, cudaStream_t s);
 cudaError_t gather_sum_launch(const float* y, const int* row_of, int k, int n, float* out, int T, cudaStream_t s);
 }  // namespace b200
