@@ -53,7 +53,7 @@ def parse_args(argv=None):
     p.add_argument("--fp8-experts", action="store_true",
                    help="convert the routed / shared expert banks to block-scaled MXFP8 at load (tcgen05 kind::mxf8f6f4); this is the "
                         "default for --quant 4/8 checkpoints (MLXB200_FP8_EXPERTS=0 keeps the exact in-kernel MLX-affine dequant)")
-    p.add_argument("--arch", type=str, default=None, choices=["perelorn"],
+    p.add_argument("--arch", type=str, default=None, choices=["perelorn", "gusolorn"],
                    help="side benchmark (bench/arch_bench.py): that design's prefill / decode throughput and kernel rooflines beside the "
                         "closest existing model; the default workload and its JSON line are not affected")
     p.add_argument("--arch-sizes", type=str, default="1024,2048", help="model widths of --arch")
@@ -122,7 +122,7 @@ def main(argv=None):
         spec = importlib.util.spec_from_file_location("arch_bench", os.path.join(os.path.dirname(os.path.abspath(__file__)), "bench", "arch_bench.py"))
         mod = importlib.util.module_from_spec(spec)
         spec.loader.exec_module(mod)
-        return mod.main(tuple(int(x) for x in args.arch_sizes.split(",")))
+        return mod.main(tuple(int(x) for x in args.arch_sizes.split(",")), args.arch)
     if args.fp8_experts:
         os.environ["MLXB200_FP8_EXPERTS"] = "1"
 

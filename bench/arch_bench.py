@@ -1,8 +1,11 @@
-"""Perelorn beside the framework's closest existing model (DeepSeek-V2 with dense feed-forwards: latent attention, same width and
+"""Hybrid designs beside the framework's closest existing model.  ``--arch gusolorn``: Gusolorn beside Perelorn (the other hybrid stack:
+latent attention + recurrent layers) at equal width and depth, and each of its kernels beside the like kernel (mLSTM scan / decayed
+linear-attention scan, windowed sink-free latent attention / latent attention with a sink, scaled residual add + norm / output-side norm +
+add, clamped-GLU experts / the SwiGLU expert path).  ``--arch perelorn``: Perelorn beside the framework's closest existing model (DeepSeek-V2 with dense feed-forwards: latent attention, same width and
 about the same weight bytes), random weights, bf16, one GPU: prefill and decode throughput of the whole stack, and the time of each
 new kernel against the HBM roofline (``MEASURED_PEAKS.json``), with the like kernel of the closest model where there is one.
 
-    python bench.py --arch perelorn [--arch-sizes 1024,2048]        (prints one JSON line per measurement)
+    python bench.py --arch perelorn|gusolorn [--arch-sizes 1024,2048]        (prints one JSON line per measurement)
 
 Timing: CUDA events on the launching stream, 3 warm-up runs, an L2 flush (256 MiB write) before every timed run, median of 7.
 """
@@ -17,7 +20,7 @@ import torch
 
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 
-from mlx_sharding_b200.config import deepseek_v2_lite_config, perelorn_config  # noqa: E402
+from mlx_sharding_b200.config import deepseek_v2_lite_config, gusolorn_config, perelorn_config  # noqa: E402
 from mlx_sharding_b200.ops.meta import BatchMeta  # noqa: E402
 from mlx_sharding_b200.parallel.pipeline import StageExecutor  # noqa: E402
 from mlx_sharding_b200.utils.loader import random_model  # noqa: E402
@@ -146,7 +149,93 @@ def kernel_table(width, dev, hbm):
     return rows
 
 
-def main(sizes=(1024, 2048)):
+def gusolorn_kernel_table(width, dev, hbm):
+    """Gusolorn's kernels alone at one layer's shapes beside the like kernel of Perelorn / DeepSeek-V2; bytes = what the kernel must move."""
+    from mlx_sharding_b200.ops import b200 as O
+    from mlx_sharding_b200.ops.weights import LinearWeight
+
+    rows = []
+    H, D, Lr, R, W = 16, 128, 512, 64, width
+    bf = torch.bfloat16
+
+    def add(name, ms, nbytes, like=None):
+        r = dict(kernel=name, ms=round(ms, 4), gbs=round(nbytes / ms / 1e6, 1), frac_hbm=round(nbytes / ms / 1e6 / hbm, 3))
+        if like:
+            r["like_kernel"] = like
+        rows.append(r)
+
+    for phase, B, q, ctx0 in (("decode", 64, 1, 2047), ("prefill", 1, 2048, 0)):
+        meta, _ = step_meta(B, q, ctx0, dev)
+        T = B * q
+        qkv = torch.randn(T, H * 4 * D, device=dev).to(bf)
+        nb = D // O.mlstm_col_block(D)
+        st = dict(S=torch.zeros(B + 1, H, D, D, device=dev), n=torch.zeros(B + 1, H, nb, D, device=dev), m=torch.zeros(B + 1, H, nb, device=dev))
+        gates, gb = torch.randn(T, 2 * H, device=dev), torch.randn(2 * H, device=dev)
+        nbytes = 2 * B * H * D * D * 4 + T * H * D * (3 * 2 + 4)
+        ms = timed(lambda: O.mlstm_scan(qkv, gates, gb, st, meta, H, D, D, 15.0, D ** -0.5))
+        add(f"mlstm_scan {phase}", ms, nbytes)
+        st2, dec = torch.zeros(B + 1, H, D, D, device=dev), torch.full((H,), 0.97, device=dev)
+        ms = timed(lambda: O.decay_scan(qkv, dec, st2, meta, H, D, D))
+        add(f"decay_scan (Perelorn) {phase}", ms, nbytes, like=f"mlstm_scan {phase}")
+        pool = torch.randn(1 + B * ((ctx0 + q + PS - 1) // PS), 1, PS, Lr + R, device=dev).to(bf)
+        qq = torch.randn(T, H, Lr + R, device=dev).to(bf)
+        sink, inv = torch.zeros(H, device=dev), torch.rand(R // 2, device=dev)
+        for win in (0, 1024):
+            seen = min(ctx0 + q, win) if win else ctx0 + q
+            nbytes = (B * seen if q == 1 else min(ctx0 + q, seen + q)) * (Lr + R) * 2 + T * H * (2 * Lr + R) * 2
+            ms = timed(lambda: O.latent_attention(qq, pool, None, meta, 0.07, Lr, inv, window=win, interleaved=True))
+            add(f"latent_attention(no sink, window {win}) {phase}", ms, nbytes)
+        ms = timed(lambda: O.latent_attention(qq, pool, sink, meta, 0.07, Lr, inv))
+        add(f"latent_attention(sink) (Perelorn) {phase}", ms, B * (ctx0 + q) * (Lr + R) * 2 + T * H * (2 * Lr + R) * 2, like=f"latent_attention(no sink, window 0) {phase}")
+        if phase == "prefill":
+            ms = timed(lambda: O.latent_attention_prefill(qq.clone(), pool, None, meta, 0.07, Lr, inv, window=1024, interleaved=True))
+            add("latent_attention_prefill(GEMM form, window 1024) prefill", ms, (ctx0 + q) * (Lr + R) * 2 + T * H * (2 * Lr + R) * 2)
+            ms = timed(lambda: O.latent_attention_prefill(qq.clone(), pool, sink, meta, 0.07, Lr, inv))
+            add("latent_attention_prefill(GEMM form, sink) (Perelorn) prefill", ms, (ctx0 + q) * (Lr + R) * 2 + T * H * (2 * Lr + R) * 2,
+                like="latent_attention_prefill(GEMM form, window 1024) prefill")
+        x, y = torch.randn(T, W, device=dev), torch.randn(T, W, device=dev)
+        ls, w = torch.randn(W, device=dev), torch.randn(W, device=dev)
+        ms = timed(lambda: O.scaled_add_norm_(x, y, ls, w, 1e-5, bf))
+        add(f"scaled_add_norm {phase}", ms, T * W * (4 + 4 + 4 + 2))
+        ms = timed(lambda: O.post_norm_add_(x, y, w, 1e-5, bf))
+        add(f"post_norm_add (Perelorn) {phase}", ms, T * W * (4 + 4 + 4 + 2), like=f"scaled_add_norm {phase}")
+        # routed experts: 16 experts, top 2, expert width 1024
+        E, F, k = 16, 1024, 2
+        xa = torch.randn(T, W, device=dev).to(bf)
+        wg, wu = (LinearWeight(weight=(torch.randn(E, F, W, device=dev) * W ** -0.5).to(bf)) for _ in range(2))
+        wd = LinearWeight(weight=(torch.randn(E, W, F, device=dev) * F ** -0.5).to(bf))
+        z = torch.randn(T, E, device=dev)
+        idx, wts = O.sigmoid_topk(z, E, k)
+        touched = min(E, T * k)
+        nbytes = touched * 3 * F * W * 2 + T * W * (2 + 4) + T * k * (2 * W * 2 + 2 * F * 2 + 2 * W * 4)
+        ms = timed(lambda: O.moe_clamped_experts(xa, idx, wts, wg, wu, wd, 7.0))
+        add(f"moe_clamped_experts {phase}", ms, nbytes)
+        ms = timed(lambda: O.moe_experts(xa, idx, wts, wg, wu, wd, "silu"))
+        add(f"moe_experts (DeepSeek-V2, SwiGLU) {phase}", ms, nbytes, like=f"moe_clamped_experts {phase}")
+        ms = timed(lambda: O.sigmoid_topk(z, E, k))
+        add(f"sigmoid_topk {phase}", ms, T * E * 4 + T * k * 8)
+    return rows
+
+
+def gusolorn_main(sizes=(1024, 2048)):
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    hbm, tag = peaks()
+    for width in sizes:
+        for name, cfg in (("gusolorn", gusolorn_config(width=width, vocab=32000, blocks=2, heads=16, ff=4 * width, experts=16, top=2, expert_ff=width // 2)),
+                          ("perelorn", perelorn_config(width=width, vocab=32000, blocks=2, heads=16, ff=4 * width, side_dim=64))):
+            m = random_model(cfg, dtype=torch.bfloat16, device=dev, seed=1)
+            r = model_runs(name, m, 32, 1024, 2048, dev, True)
+            print(json.dumps(dict(bench="arch", model=name, width=width, layers=len(cfg["layers"]), **{k: (round(v, 3) if isinstance(v, float) else v) for k, v in r.items()})), flush=True)
+            del m
+            torch.cuda.empty_cache()
+    for row in gusolorn_kernel_table(sizes[-1], dev, hbm):
+        print(json.dumps(dict(bench="arch-kernel", roofline=f"{hbm} GB/s {tag}", **row)), flush=True)
+
+
+def main(sizes=(1024, 2048), arch="perelorn"):
+    if arch == "gusolorn":
+        return gusolorn_main(sizes)
     dev = torch.device("cuda", 0)
     torch.cuda.set_device(dev)
     hbm, tag = peaks()
@@ -172,4 +261,4 @@ def main(sizes=(1024, 2048)):
 
 
 if __name__ == "__main__":
-    main(tuple(int(x) for x in sys.argv[1].split(",")) if len(sys.argv) > 1 else (1024, 2048))
+    main(tuple(int(x) for x in sys.argv[1].split(",")) if len(sys.argv) > 1 else (1024, 2048), sys.argv[2] if len(sys.argv) > 2 else "perelorn")

@@ -114,16 +114,14 @@ class GusolornStage(StageModel):
                     w.update(up=self._lw(sd.pop(p + "mlp.up")), down=self._lw(sd.pop(p + "mlp.down")))
                 else:
                     E = int(mlp["router"]["experts"])
-                    gu = torch.stack([torch.cat([sd.pop(p + f"mlp.e{e}.gate"), sd.pop(p + f"mlp.e{e}.up")]) for e in range(E)])
-                    dn = torch.stack([sd.pop(p + f"mlp.e{e}.down") for e in range(E)])
-                    w.update(e_gu=LinearWeight(weight=gu.to(device=dev, dtype=self.dtype).contiguous()),
-                             e_down=LinearWeight(weight=dn.to(device=dev, dtype=self.dtype).contiguous()))
+                    bank = lambda n: LinearWeight(weight=torch.stack([sd.pop(p + f"mlp.e{e}.{n}") for e in range(E)]).to(device=dev, dtype=self.dtype).contiguous())
+                    w.update(e_gate=bank("gate"), e_up=bank("up"), e_down=bank("down"))
                     rows = [sd.pop(p + "mlp.router")]
                     if mlp.get("shared"):
                         # the always-on expert's gate logit rides along with the router logits: one fp32 product [experts + 1, width]
                         rows.append(sd.pop(p + "mlp.shared.sg"))
-                        w.update(s_gu=self._lw(torch.cat([sd.pop(p + "mlp.shared.gate"), sd.pop(p + "mlp.shared.up")])),
-                                 s_down=self._lw(sd.pop(p + "mlp.shared.down")))
+                        raw = lambda n: LinearWeight(weight=sd.pop(p + "mlp.shared." + n).to(device=dev, dtype=self.dtype).contiguous())
+                        w.update(s_gate=raw("gate"), s_up=raw("up"), s_down=self._lw(sd.pop(p + "mlp.shared.down")))
                     w["router"] = torch.cat(rows).to(device=dev, dtype=torch.float32).contiguous()
             self.layer_weights[i] = w
         self.norm_w = self._norm_w(sd, "final.norm")
@@ -168,10 +166,10 @@ class GusolornStage(StageModel):
         E, top = int(mlp["router"]["experts"]), int(mlp["router"]["top"])
         z = O.router_logits(ha, w["router"])                                          # fp32 [T, E (+1)]
         idx, wts = O.sigmoid_topk(z, E, top)
-        y = O.moe_clamped_experts(ha, idx, wts, w["e_gu"], w["e_down"], float(mlp["expert"]["limit"]))
-        if "s_gu" not in w:
+        y = O.moe_clamped_experts(ha, idx, wts, w["e_gate"], w["e_up"], w["e_down"], float(mlp["expert"]["limit"]))
+        if "s_gate" not in w:
             return y, None, None
-        hs = O.clamped_glu(self._mm(ha, w["s_gu"]), float(mlp["shared"]["limit"]), self.dtype)
+        hs = O.clamped_gated_up(ha, w["s_gate"], w["s_up"], float(mlp["shared"]["limit"]))
         return y, self._mm(hs, w["s_down"], True), z[:, E]
 
     def layer_forward(self, i, h, ha, meta, kv, next_norm):

@@ -616,31 +616,49 @@ def sigmoid_topk(z, num_experts: int, top: int):
     return idx, w
 
 
-def clamped_glu(gu, limit: float, out_dtype=None, row_scale=None):
-    return C().hy_clamped_glu(gu, float(limit), None, row_scale)
+ACT_CLAMPED_GLU = 3      # two-weight GEMM epilogue: min(g, limit) sigmoid(1.702 .) (clamp(u, +-limit) + 1)
 
 
-def moe_clamped_experts(x, idx, w, Wgu: LinearWeight, Wd: LinearWeight, limit: float):
-    """Routed clamped-GLU experts, router weight on the expert's input (applied to the gate / up products, which are linear in it):
-    counting-sort permutation -> grouped gate|up GEMM -> clamped GLU -> grouped down GEMM (fp32) -> sum per token.  bf16 banks whose
-    sizes fit the grouped tcgen05 GEMM (rows multiples of 128, inner sizes multiples of 8) take it; exact mode (fp32) and other sizes
-    run one cuBLAS product per expert on the sorted rows."""
+def clamped_glu(g, u, limit: float, out_dtype=None, row_scale=None):
+    return C().hy_clamped_glu(g, u, float(limit), None, row_scale)
+
+
+def _tc_ok(x, *ws) -> bool:
+    """bf16 operands that satisfy the tensor-core GEMM's TMA rules (inner size and output rows multiples of 8, 16-byte aligned rows)."""
+    return (x.dtype == torch.bfloat16 and x.shape[0] > 0 and x.shape[1] % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0
+            and x.data_ptr() % 16 == 0 and all(w.dtype == torch.bfloat16 and w.shape[-2] % 8 == 0 for w in ws))
+
+
+def clamped_gated_up(x, Wg: LinearWeight, Wu: LinearWeight, limit: float):
+    """Both projections and the clamped GLU in ONE tcgen05 GEMM (two accumulators in TMEM, activation in the epilogue); exact mode and
+    odd sizes: two cuBLAS products and the elementwise kernel."""
+    if _tc_ok(x, Wg.weight, Wu.weight):
+        return C().linear(x, Wg.weight, Wu.weight, None, None, ACT_CLAMPED_GLU, 0.0, False, None, 0, 0, 0, float(limit))
+    lin = torch.nn.functional.linear
+    return C().hy_clamped_glu(lin(x, Wg.weight), lin(x, Wu.weight), float(limit), None, None)
+
+
+def moe_clamped_experts(x, idx, w, Wg: LinearWeight, Wu: LinearWeight, Wd: LinearWeight, limit: float):
+    """Routed clamped-GLU experts with the router weight on the expert's input.  bf16 banks whose sizes fit the grouped tcgen05 GEMM
+    (expert rows multiples of 128, inner sizes multiples of 8): counting-sort permutation that scales each gathered row by its pair's
+    weight -> grouped two-weight GEMM with the clamped GLU in its epilogue -> grouped down GEMM (fp32) -> sum per token.  Exact mode
+    (fp32) and other sizes apply the weight to the gate / up products (linear in the input) and run either one weight-row read per
+    (token, choice) pair (few rows; anything inside a graph capture) or one cuBLAS product per expert on the sorted rows."""
     c = C()
     T, k = idx.shape
-    wgu, wd = Wgu.weight, Wd.weight
-    E, F2, K = wgu.shape
-    if x.dtype == torch.bfloat16 and F2 % 128 == 0 and K % 128 == 0 and (F2 // 2) % 8 == 0 and x.stride(1) == 1 and x.stride(0) % 8 == 0:
-        offs, pair_row, xp = c.moe_permute(idx, x, E)
-        gu = c.grouped_linear(xp, wgu, None, offs, T, 0, False)
-        h = c.hy_clamped_glu(gu, float(limit), pair_row, w.reshape(-1))
+    wg, wu, wd = Wg.weight, Wu.weight, Wd.weight
+    E, F, K = wg.shape
+    wflat = w.reshape(-1).contiguous()
+    if _tc_ok(x) and wg.dtype == torch.bfloat16 and F % 128 == 0 and K % 128 == 0:
+        offs, pair_row, xp = c.moe_permute(idx, x, E, wflat)
+        h = c.grouped_linear(xp, wg, wu, offs, T, ACT_CLAMPED_GLU, False, act_limit=float(limit))
         y = c.grouped_linear(h, wd, None, offs, T, 0, True)
         return c.hy_gather_sum(y, pair_row, int(k))
     R = T * k
     if R <= PAIR_KERNEL_MAX_ROWS or torch.cuda.is_current_stream_capturing():
-        # few rows (decode steps; anything inside a graph capture): every (token, choice) pair reads its expert's rows itself
         ids = idx.reshape(-1).contiguous()
-        gu = c.hy_expert_rows_linear(x, int(k), wgu, ids, False)
-        h = c.hy_clamped_glu(gu, float(limit), None, w.reshape(-1).contiguous())
+        h = c.hy_clamped_glu(c.hy_expert_rows_linear(x, int(k), wg, ids, False), c.hy_expert_rows_linear(x, int(k), wu, ids, False),
+                             float(limit), None, wflat)
         y = c.hy_expert_rows_linear(h, 1, wd, ids, True)
         return y if k == 1 else y.view(T, k, K).sum(1)
     flat = idx.reshape(-1).long()
@@ -649,14 +667,15 @@ def moe_clamped_experts(x, idx, w, Wgu: LinearWeight, Wd: LinearWeight, limit: f
     pair_row[order] = torch.arange(order.numel(), device=x.device, dtype=torch.int32)
     xp = gather_rows(x, (order // k).contiguous(), 0, K, x.dtype)
     counts = torch.bincount(flat, minlength=E).tolist()
-    gu = torch.empty(xp.shape[0], F2, dtype=x.dtype, device=x.device)
+    g, u = torch.empty(R, F, dtype=x.dtype, device=x.device), torch.empty(R, F, dtype=x.dtype, device=x.device)
     r0 = 0
     for e, n in enumerate(counts):
         if n:
-            torch.matmul(xp[r0:r0 + n], wgu[e].t(), out=gu[r0:r0 + n])
+            torch.matmul(xp[r0:r0 + n], wg[e].t(), out=g[r0:r0 + n])
+            torch.matmul(xp[r0:r0 + n], wu[e].t(), out=u[r0:r0 + n])
         r0 += n
-    h = c.hy_clamped_glu(gu, float(limit), pair_row, w.reshape(-1).contiguous())
-    y = torch.empty(xp.shape[0], K, dtype=torch.float32, device=x.device)
+    h = c.hy_clamped_glu(g, u, float(limit), pair_row, wflat)
+    y = torch.empty(R, K, dtype=torch.float32, device=x.device)
     r0 = 0
     for e, n in enumerate(counts):
         if n:

@@ -99,7 +99,7 @@ int auto_splits(int rows, int n, int k, bool grouped) {
 // ---- GEMM -------------------------------------------------------------------------------------------------------
 Tensor linear(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& w2, const c10::optional<Tensor>& residual,
               const c10::optional<Tensor>& bias, int64_t act, double softcap, bool out_fp32, const c10::optional<Tensor>& out_,
-              int64_t splits, int64_t signal_flag_ptr, int64_t signal_value) {
+              int64_t splits, int64_t signal_flag_ptr, int64_t signal_value, double act_limit) {
   check_bf16(x, "x"); check_bf16(w, "w"); check_rows(x, "x"); check_rows(w, "w");
   const c10::cuda::CUDAGuard guard(x.device());
   const int64_t T = x.size(0), K = x.size(1), N = w.size(0);
@@ -115,7 +115,7 @@ Tensor linear(const Tensor& x, const Tensor& w, const c10::optional<Tensor>& w2,
   a.out = out.data_ptr(); a.ld_out = out.stride(0); a.out_fp32 = out.scalar_type() == torch::kFloat32;
   if (residual.has_value()) { check_bf16(*residual, "residual"); check_rows(*residual, "residual"); a.residual = residual->data_ptr(); a.ld_res = residual->stride(0); }
   if (bias.has_value()) { check_bf16(*bias, "bias"); a.bias = bias->data_ptr(); }
-  a.act = (int)act; a.softcap = (float)softcap;
+  a.act = (int)act; a.act_limit = (float)act_limit; a.softcap = (float)softcap;
   int sp = splits > 0 ? (int)splits : auto_splits((int)T, (int)N, (int)K, false);
   a.splits = sp;
   auto& sc = scratch();
@@ -139,7 +139,7 @@ Tensor grouped_linear(const Tensor& x, const Tensor& w, const c10::optional<Tens
                       int64_t max_rows, int64_t act, bool out_fp32, const c10::optional<Tensor>& row_dst,
                       const c10::optional<Tensor>& signal_peers, const c10::optional<Tensor>& done_counter, int64_t expected_rows,
                       int64_t expert_stride, int64_t ep_arrive_ptr, const c10::optional<Tensor>& ep_seq, int64_t ep_error_ptr,
-                      int64_t ep_world, bool ep_zero_other) {
+                      int64_t ep_world, bool ep_zero_other, double act_limit) {
   check_bf16(x, "x"); check_bf16(w, "w"); check_rows(x, "x");
   TORCH_CHECK(w.dim() == 3 && w.is_contiguous(), "w must be contiguous [E, N, K]");
   const c10::cuda::CUDAGuard guard(x.device());
@@ -178,7 +178,7 @@ Tensor grouped_linear(const Tensor& x, const Tensor& w, const c10::optional<Tens
   // smaller token-tile loads; experts with more rows simply take further tiles of the persistent tile list
   // expected_rows (>0): the caller's estimate of the rows actually present when x is an over-sized buffer (EP receive side)
   a.bn = grouped_bn(a.max_rows, expected_rows > 0 ? expected_rows : R, E);
-  a.out = out.data_ptr(); a.ld_out = N; a.out_fp32 = out_fp32; a.act = (int)act; a.splits = 1;
+  a.out = out.data_ptr(); a.ld_out = N; a.out_fp32 = out_fp32; a.act = (int)act; a.act_limit = (float)act_limit; a.splits = 1;
   LAUNCH_OK(b200::gemm_launch(a, cur_stream()));
   return out;
 }
@@ -525,7 +525,9 @@ std::vector<Tensor> moe_route(const Tensor& x, const Tensor& gate_w, int64_t top
   return {idx, w};
 }
 
-std::vector<Tensor> moe_permute(const Tensor& idx, const Tensor& x, int64_t E) {
+std::vector<Tensor> moe_permute(const Tensor& idx, const Tensor& x, int64_t E, const c10::optional<Tensor>& pair_scale) {
+  TORCH_CHECK(!pair_scale.has_value() || (pair_scale->is_cuda() && pair_scale->scalar_type() == torch::kFloat32 && pair_scale->is_contiguous() &&
+                                          pair_scale->numel() == idx.numel()), "pair_scale must be contiguous float32, one per (token, choice)");
   check_bf16(x, "x"); check_rows(x, "x");
   TORCH_CHECK(idx.scalar_type() == torch::kInt32 && idx.is_contiguous());
   const c10::cuda::CUDAGuard guard(x.device());
@@ -534,7 +536,8 @@ std::vector<Tensor> moe_permute(const Tensor& idx, const Tensor& x, int64_t E) {
   Tensor offs = torch::empty({E + 1}, io), pair_row = torch::empty({T * k}, io);
   Tensor xp = torch::empty({(int64_t)T * k, H}, x.options());
   LAUNCH_OK(b200::moe_permute_launch(idx.data_ptr<int>(), T, k, (int)E, offs.data_ptr<int>(), pair_row.data_ptr<int>(), nullptr,
-                                   x.data_ptr(), x.stride(0), xp.data_ptr(), H, cur_stream()));
+                                   x.data_ptr(), x.stride(0), xp.data_ptr(), H, cur_stream(),
+                                   pair_scale.has_value() ? pair_scale->data_ptr<float>() : nullptr));
   ++g_launches;  // offsets + gather
   return {offs, pair_row, xp};
 }
@@ -1037,18 +1040,19 @@ std::vector<Tensor> hy_sigmoid_topk(const Tensor& z, int64_t E, int64_t top) {
   return {idx, w};
 }
 
-// row_of / scale (both optional, one entry per processed row): block i handles row row_of[i] of gu with scale[i]
-Tensor hy_clamped_glu(const Tensor& gu, double limit, const c10::optional<Tensor>& row_of, const c10::optional<Tensor>& scale) {
-  check_act(gu, "gu"); check_rows(gu, "gu");
-  TORCH_CHECK(gu.dim() == 2 && gu.size(1) % 2 == 0);
-  const int64_t F = gu.size(1) / 2, rows = row_of.has_value() ? row_of->numel() : gu.size(0);
+// row_of / scale (both optional, one entry per processed row): block i handles row row_of[i] of g and u with scale[i]
+Tensor hy_clamped_glu(const Tensor& g, const Tensor& u, double limit, const c10::optional<Tensor>& row_of, const c10::optional<Tensor>& scale) {
+  check_act(g, "gate"); check_rows(g, "gate"); check_act(u, "up"); check_rows(u, "up");
+  TORCH_CHECK(g.dim() == 2 && u.sizes() == g.sizes() && u.scalar_type() == g.scalar_type());
+  const int64_t F = g.size(1), rows = row_of.has_value() ? row_of->numel() : g.size(0);
   if (row_of.has_value()) check_i32(*row_of, "row_of");
   if (scale.has_value()) { check_f32c(*scale, "scale"); TORCH_CHECK(scale->numel() == rows); }
-  const c10::cuda::CUDAGuard guard(gu.device());
-  Tensor out = torch::empty({gu.size(0), F}, gu.options());
+  const c10::cuda::CUDAGuard guard(g.device());
+  Tensor out = torch::empty({g.size(0), F}, g.options());
   if (rows == 0) return out;
-  LAUNCH_OK(b200::clamped_glu_launch(gu.data_ptr(), gu.stride(0), (int)F, (float)limit, row_of.has_value() ? row_of->data_ptr<int>() : nullptr,
-                                     scale.has_value() ? scale->data_ptr<float>() : nullptr, out.data_ptr(), is_f32(gu), (int)rows, cur_stream()));
+  LAUNCH_OK(b200::clamped_glu_launch(g.data_ptr(), g.stride(0), u.data_ptr(), u.stride(0), (int)F, (float)limit,
+                                     row_of.has_value() ? row_of->data_ptr<int>() : nullptr, scale.has_value() ? scale->data_ptr<float>() : nullptr,
+                                     out.data_ptr(), is_f32(g), (int)rows, cur_stream()));
   return out;
 }
 
@@ -1082,12 +1086,12 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.doc() = "mlx_sharding_b200 sm_100a kernels";
   m.def("linear", &linear, py::arg("x"), py::arg("w"), py::arg("w2") = py::none(), py::arg("residual") = py::none(),
         py::arg("bias") = py::none(), py::arg("act") = 0, py::arg("softcap") = 0.0, py::arg("out_fp32") = false,
-        py::arg("out") = py::none(), py::arg("splits") = 0, py::arg("signal_flag_ptr") = 0, py::arg("signal_value") = 0);
+        py::arg("out") = py::none(), py::arg("splits") = 0, py::arg("signal_flag_ptr") = 0, py::arg("signal_value") = 0, py::arg("act_limit") = 0.0);
   m.def("grouped_linear", &grouped_linear, py::arg("x"), py::arg("w"), py::arg("w2") = py::none(), py::arg("expert_offsets"),
         py::arg("max_rows"), py::arg("act") = 0, py::arg("out_fp32") = false, py::arg("row_dst") = py::none(),
         py::arg("signal_peers") = py::none(), py::arg("done_counter") = py::none(), py::arg("expected_rows") = 0,
         py::arg("expert_stride") = 0, py::arg("ep_arrive_ptr") = 0, py::arg("ep_seq") = py::none(), py::arg("ep_error_ptr") = 0,
-        py::arg("ep_world") = 0, py::arg("ep_zero_other") = false);
+        py::arg("ep_world") = 0, py::arg("ep_zero_other") = false, py::arg("act_limit") = 0.0);
   m.def("linear_q", &linear_q);
   m.def("grouped_linear_q", &grouped_linear_q);
   m.def("gemm_q_supported", &gemm_q_supported);
@@ -1113,7 +1117,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
   m.def("moe_route", &moe_route, py::arg("x"), py::arg("gate_w"), py::arg("top_k"), py::arg("n_group"), py::arg("topk_group"),
         py::arg("scaling"), py::arg("norm_topk"), py::arg("extra") = 0, py::arg("sc_counts") = py::none(), py::arg("sc_stride") = 0,
         py::arg("sc_x") = py::none(), py::arg("norm_w") = py::none(), py::arg("norm_eps") = 1e-6);
-  m.def("moe_permute", &moe_permute);
+  m.def("moe_permute", &moe_permute, py::arg("idx"), py::arg("x"), py::arg("E"), py::arg("pair_scale") = py::none());
   m.def("moe_combine", &moe_combine, py::arg("y_perm"), py::arg("pair_row"), py::arg("wts"), py::arg("residual") = py::none(),
         py::arg("out") = py::none(), py::arg("top_k"), py::arg("signal_flag_ptr") = 0, py::arg("signal_value") = 0,
         py::arg("zero_counts") = py::none(), py::arg("norm_w") = py::none(), py::arg("norm_eps") = 1e-6, py::arg("normed") = py::none());
@@ -1170,7 +1174,7 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
         py::arg("extra") = py::none(), py::arg("gate") = py::none());
   m.def("hy_mlstm_scan", &hy_mlstm_scan);
   m.def("hy_sigmoid_topk", &hy_sigmoid_topk);
-  m.def("hy_clamped_glu", &hy_clamped_glu, py::arg("gu"), py::arg("limit"), py::arg("row_of") = py::none(), py::arg("scale") = py::none());
+  m.def("hy_clamped_glu", &hy_clamped_glu, py::arg("gate"), py::arg("up"), py::arg("limit"), py::arg("row_of") = py::none(), py::arg("scale") = py::none());
   m.def("hy_gather_sum", &hy_gather_sum);
   m.def("hy_expert_rows_linear", &hy_expert_rows_linear);
   m.def("pdl_skip_next", []() { b200::pdl_skip_next(); });

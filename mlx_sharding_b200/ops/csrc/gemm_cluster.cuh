@@ -96,7 +96,7 @@ __device__ __forceinline__ void cluster_epilogue_reduce_store(const GemmParams& 
       }
     }
     float y = g + bias;
-    if (DUAL) y = apply_act(p.act, y) * u;
+    if (DUAL) y = gated_act(p.act, p.act_limit, y, u);
     if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
     if (f_glob < p.n) {
       const size_t row = static_cast<size_t>(row_base + t);

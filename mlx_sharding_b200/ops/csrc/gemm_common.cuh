@@ -43,6 +43,16 @@ __device__ __forceinline__ float apply_act(int act, float g) {
   return g;
 }
 
+// act(gate) * up of the two-weight GEMMs
+__device__ __forceinline__ float gated_act(int act, float limit, float g, float u) {
+  if (act == kActClampedGlu) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit);
+    return g / (1.0f + __expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return apply_act(act, g) * u;
+}
+
 template <typename OutT>
 __device__ __forceinline__ void stage_store(OutT* p, float v);
 template <>
@@ -149,7 +159,7 @@ __device__ __forceinline__ void run_epilogue(const GemmParams& p, uint8_t* smem,
 #pragma unroll
         for (int j = 0; j < 16; ++j) {
           float y = g[j] + bias;
-          if (DUAL) y = apply_act(p.act, y) * u[j];
+          if (DUAL) y = gated_act(p.act, p.act_limit, y, u[j]);
           if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
           stage_store<OutT>(&stg[(c + j) * kTileM + f_local], y);
         }

@@ -283,7 +283,7 @@ gemm_persistent_kernel(const __grid_constant__ CUtensorMap tmap_w, const __grid_
 #pragma unroll
           for (int j = 0; j < 16; ++j) {
             float y = g[j] + bias;
-            if (DUAL) y = apply_act(p.act, y) * u[j];
+            if (DUAL) y = gated_act(p.act, p.act_limit, y, u[j]);
             if (p.softcap > 0.f) y = p.softcap * tanhf(y / p.softcap);
             stage_store<OutT>(&stg[(c - c0 + j) * kTileM + f_local], y);
           }
@@ -427,7 +427,7 @@ cudaError_t gemm_persistent_launch(const GemmArgs& a, cudaStream_t stream) {
   p.expert_stride = a.expert_stride;
   p.out = a.out; p.ld_out = a.ld_out;
   p.residual = static_cast<const __nv_bfloat16*>(a.residual); p.ld_res = a.ld_res;
-  p.bias = static_cast<const __nv_bfloat16*>(a.bias); p.act = a.act; p.softcap = a.softcap;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias); p.act = a.act; p.act_limit = a.act_limit; p.softcap = a.softcap;
   p.workspace = nullptr; p.tile_counters = nullptr;
   p.signal_flag = a.signal_flag; p.signal_value = a.signal_value; p.done_counter = a.done_counter;
   const int tiles_n = (a.n + kTileM - 1) / kTileM;

@@ -358,7 +358,7 @@ cudaError_t gemm_launch(const GemmArgs& a, cudaStream_t stream) {
   p.expert_stride = a.expert_stride;
   p.out = a.out; p.ld_out = a.ld_out;
   p.residual = static_cast<const __nv_bfloat16*>(a.residual); p.ld_res = a.ld_res;
-  p.bias = static_cast<const __nv_bfloat16*>(a.bias); p.act = a.act; p.softcap = a.softcap;
+  p.bias = static_cast<const __nv_bfloat16*>(a.bias); p.act = a.act; p.act_limit = a.act_limit; p.softcap = a.softcap;
   p.workspace = a.workspace; p.tile_counters = a.tile_counters;
   p.signal_flag = a.signal_flag; p.signal_value = a.signal_value; p.done_counter = a.done_counter;
 

@@ -7,7 +7,8 @@
 
 namespace b200 {
 
-enum : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2 };
+// kActClampedGlu (two-weight form only): g' = min(g, act_limit), u' = clamp(u, +-act_limit), y = g' sigmoid(1.702 g') (u' + 1)
+enum : int { kActNone = 0, kActSilu = 1, kActGeluTanh = 2, kActClampedGlu = 3 };
 
 // Device-side parameter block (passed by value).
 struct GemmParams {
@@ -26,6 +27,7 @@ struct GemmParams {
   long long ld_res;
   const __nv_bfloat16* bias;
   int act;
+  float act_limit;
   float softcap;
   float* workspace;
   unsigned int* tile_counters;
@@ -62,6 +64,7 @@ struct GemmArgs {
   long long ld_res = 0;
   const void* bias = nullptr;     // bf16 [n]
   int act = kActNone;             // used with w2
+  float act_limit = 0.f;          // clamp of kActClampedGlu
   float softcap = 0.f;            // y = cap * tanh(y / cap) (Gemma-2 final logits)
   int bn = 0;                     // token tile (0 = auto)
   int splits = 1;                 // split-K factor

@@ -685,16 +685,17 @@ __global__ void sigmoid_topk_kernel(const float* __restrict__ z, long long ld_z,
   }
 }
 
-// [g | u] rows (F each) -> g' sigmoid(1.702 g') (u' + 1),  g' = min(s g, limit), u' = clamp(s u, +-limit).  Block i handles row
+// gate rows g and up rows u (F wide each, own row strides) -> g' sigmoid(1.702 g') (u' + 1),  g' = min(s g, limit), u' = clamp(s u, +-limit).  Block i handles row
 // row_of[i] with scale s = scale[i] (both nullable: row i, scale 1): scaling a projection's output equals scaling its input.
 template <typename AT>
-__global__ void clamped_glu_kernel(const AT* __restrict__ gu, long long ld, int F, float limit, const int* __restrict__ row_of,
-                                   const float* __restrict__ scale, AT* __restrict__ out) {
+__global__ void clamped_glu_kernel(const AT* __restrict__ gp, long long ld_g, const AT* __restrict__ up, long long ld_u, int F, float limit,
+                                   const int* __restrict__ row_of, const float* __restrict__ scale, AT* __restrict__ out) {
   const long long r = row_of != nullptr ? row_of[blockIdx.x] : blockIdx.x;
   const float s = scale != nullptr ? scale[blockIdx.x] : 1.f;
-  const AT* row = gu + r * ld;
+  const AT* grow = gp + r * ld_g;
+  const AT* urow = up + r * ld_u;
   for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < F; c += gridDim.y * blockDim.x) {
-    const float g = fminf(s * ldf<AT>(row + c), limit), u = fminf(fmaxf(s * ldf<AT>(row + F + c), -limit), limit);
+    const float g = fminf(s * ldf<AT>(grow + c), limit), u = fminf(fmaxf(s * ldf<AT>(urow + c), -limit), limit);
     stf<AT>(out + r * F + c, g * sigmoid_f(1.702f * g) * (u + 1.f));
   }
 }
@@ -906,10 +907,10 @@ cudaError_t sigmoid_topk_launch(const float* z, long long ld_z, int E, int top, 
   return last();
 }
 
-cudaError_t clamped_glu_launch(const void* gu, long long ld, int F, float limit, const int* row_of, const float* scale, void* out, bool f32,
-                               int rows, cudaStream_t s) {
+cudaError_t clamped_glu_launch(const void* g, long long ld_g, const void* u, long long ld_u, int F, float limit, const int* row_of,
+                               const float* scale, void* out, bool f32, int rows, cudaStream_t s) {
   dim3 grid(rows, (F + 1023) / 1024);
-  AT_DISPATCH(f32, (clamped_glu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)gu, ld, F, limit, row_of, scale, (AT*)out)));
+  AT_DISPATCH(f32, (clamped_glu_kernel<AT><<<grid, 256, 0, s>>>((const AT*)g, ld_g, (const AT*)u, ld_u, F, limit, row_of, scale, (AT*)out)));
   return last();
 }
 

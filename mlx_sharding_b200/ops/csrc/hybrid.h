@@ -40,8 +40,8 @@ cudaError_t mlstm_scan_launch(const void* in, long long ld_in, const float* gate
                               float* m, const int* cu, const int* ctx, const int* slots, float* out, int B, int H, int N, int P, int PB,
                               float cap, float q_scale, bool f32, int max_q, cudaStream_t s);
 cudaError_t sigmoid_topk_launch(const float* z, long long ld_z, int E, int top, int* idx, float* w, int T, cudaStream_t s);
-cudaError_t clamped_glu_launch(const void* gu, long long ld, int F, float limit, const int* row_of, const float* scale, void* out, bool f32,
-                               int rows, cudaStream_t s);
+cudaError_t clamped_glu_launch(const void* g, long long ld_g, const void* u, long long ld_u, int F, float limit, const int* row_of,
+                               const float* scale, void* out, bool f32, int rows, cudaStream_t s);
 cudaError_t expert_rows_linear_launch(const void* x, long long ld_x, int div, const void* W, const int* expert, int N, int K, void* out, bool f32,
                                       bool out_f32, int rows, cudaStream_t s);
 cudaError_t gather_sum_launch(const float* y, const int* row_of, int k, int n, float* out, int T, cudaStream_t s);

@@ -99,7 +99,7 @@ cudaError_t moe_route_launch(const void* x, long long ld_x, const void* gate_w, 
 // permutation: counts/offsets per expert, destination row of every (token, k) pair, gathered rows
 cudaError_t moe_permute_launch(const int* idx, int T, int top_k, int E, int* expert_offsets /*E+1*/, int* pair_row /*T*k*/,
                                int* counters /*E scratch*/, const void* x, long long ld_x, void* x_perm, int H,
-                               cudaStream_t s);
+                               cudaStream_t s, const float* pair_scale = nullptr /*T*k: multiplies the gathered rows*/);
 // y[t] = sum_k w[t,k] * y_perm[pair_row[t,k]] (+ residual[t]); out may be a peer pointer; optional release flag
 cudaError_t moe_combine_launch(const void* y_perm, const int* pair_row, const float* wts, const void* residual,
                                long long ld_res, void* out, long long ld_out, int T, int top_k, int H,

@@ -299,8 +299,9 @@ moe_offsets_kernel(const int* __restrict__ idx, int npairs, int E, int* __restri
   for (int p = threadIdx.x; p < npairs; p += blockDim.x) pair_row[p] = atomicAdd(&cur[idx[p]], 1);
 }
 
+// pair_scale (nullable, one fp32 per (token, choice) pair): the gathered row is multiplied by it (router weight on an expert's INPUT)
 __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long ld_x, const int* __restrict__ pair_row,
-                                  __nv_bfloat16* __restrict__ x_perm, int H, int top_k, long long total) {
+                                  __nv_bfloat16* __restrict__ x_perm, int H, int top_k, long long total, const float* __restrict__ pair_scale) {
   pdl_sync();  // PDL: predecessor's writes visible; let the successor start its prologue
   const int nvec = H / 8;
   const long long i = blockIdx.x * (long long)blockDim.x + threadIdx.x;
@@ -308,8 +309,17 @@ __global__ void moe_gather_kernel(const __nv_bfloat16* __restrict__ x, long long
   const int v = i % nvec;
   const long long p = i / nvec;
   const int t = p / top_k;
-  reinterpret_cast<uint4*>(x_perm + (size_t)pair_row[p] * H)[v] =
-      reinterpret_cast<const uint4*>(x + (size_t)t * ld_x)[v];
+  uint4 val = reinterpret_cast<const uint4*>(x + (size_t)t * ld_x)[v];
+  if (pair_scale != nullptr) {
+    const float sc = pair_scale[p];
+    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&val);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h2[i]);
+      h2[i] = __floats2bfloat162_rn(f.x * sc, f.y * sc);
+    }
+  }
+  reinterpret_cast<uint4*>(x_perm + (size_t)pair_row[p] * H)[v] = val;
 }
 
 // ------------------------------------------------------------------------------------------------ combine
@@ -507,7 +517,7 @@ cudaError_t moe_route_launch(const void* x, long long ld_x, const void* gate_w, 
 }
 
 cudaError_t moe_permute_launch(const int* idx, int T, int top_k, int E, int* expert_offsets, int* pair_row, int* counters,
-                               const void* x, long long ld_x, void* x_perm, int H, cudaStream_t s) {
+                               const void* x, long long ld_x, void* x_perm, int H, cudaStream_t s, const float* pair_scale) {
   (void)counters;
   if (T == 0) return cudaSuccess;
   if (E > 256 || (H % 8)) return cudaErrorInvalidValue;
@@ -516,7 +526,7 @@ cudaError_t moe_permute_launch(const int* idx, int T, int top_k, int E, int* exp
   if (e != cudaSuccess) return e;
   const long long total = (long long)T * top_k * (H / 8);
   (void)launch_pdl(moe_gather_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, s, static_cast<const __nv_bfloat16*>(x), ld_x, pair_row,
-                                                                    static_cast<__nv_bfloat16*>(x_perm), H, top_k, total);
+                                                                    static_cast<__nv_bfloat16*>(x_perm), H, top_k, total, pair_scale);
   return cudaGetLastError();
 }
 

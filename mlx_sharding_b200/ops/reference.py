@@ -580,29 +580,34 @@ def sigmoid_topk(z: torch.Tensor, num_experts: int, top: int) -> Tuple[torch.Ten
     return order.to(torch.int32), torch.gather(sc, 1, order)
 
 
-def clamped_glu(gu: torch.Tensor, limit: float, out_dtype: torch.dtype, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """``[g | u]`` ``[R, 2F]`` -> ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(s g, limit)``, ``u' = clamp(s u, +-limit)``; ``s`` =
-    ``row_scale`` (per row, default 1): scaling a linear projection's output equals scaling its input."""
-    Fh = gu.shape[1] // 2
-    g, u = gu[:, :Fh].float(), gu[:, Fh:].float()
+def clamped_glu(g: torch.Tensor, u: torch.Tensor, limit: float, out_dtype: torch.dtype, row_scale: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gate rows ``g`` and up rows ``u`` ``[R, F]`` -> ``g' sigmoid(1.702 g') (u' + 1)`` with ``g' = min(s g, limit)``, ``u' = clamp(s u,
+    +-limit)``; ``s`` = ``row_scale`` (per row, default 1): scaling a linear projection's output equals scaling its input."""
+    g, u = g.float(), u.float()
     if row_scale is not None:
         g, u = g * row_scale.float()[:, None], u * row_scale.float()[:, None]
     g, u = g.clamp(max=limit), u.clamp(-limit, limit)
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)).to(out_dtype)
 
 
-def moe_clamped_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wgu: LinearWeight, Wd: LinearWeight, limit: float) -> torch.Tensor:
+def clamped_gated_up(x: torch.Tensor, Wg: LinearWeight, Wu: LinearWeight, limit: float) -> torch.Tensor:
+    """First half of a clamped-GLU feed-forward: :func:`clamped_glu` of ``x Wg^T`` and ``x Wu^T`` (one fused GEMM on the b200 backend)."""
+    return clamped_glu(linear(x, Wg, out_dtype=torch.float32), linear(x, Wu, out_dtype=torch.float32), limit, x.dtype)
+
+
+def moe_clamped_experts(x: torch.Tensor, idx: torch.Tensor, w: torch.Tensor, Wg: LinearWeight, Wu: LinearWeight, Wd: LinearWeight,
+                        limit: float) -> torch.Tensor:
     """``y[t] = sum_j expert_{idx[t,j]}(w[t,j] x[t])`` with clamped-GLU experts (:func:`clamped_glu`): the router weight scales the
-    expert's INPUT.  ``Wgu`` ``[E, 2F, K]`` (gate rows then up rows), ``Wd`` ``[E, K, F]``.  Returns fp32 ``[T, K]``."""
+    expert's INPUT.  Banks ``Wg``, ``Wu`` ``[E, F, K]``, ``Wd`` ``[E, K, F]``.  Returns fp32 ``[T, K]``."""
     T, k = idx.shape
     y = torch.zeros(T, Wd.weight.shape[1], dtype=torch.float32, device=x.device)
     il = idx.long()
-    for e in range(Wgu.weight.shape[0]):
+    for e in range(Wg.weight.shape[0]):
         tok, slot = torch.where(il == e)
         if tok.numel() == 0:
             continue
-        gu = x[tok].float() @ Wgu.weight[e].float().t()
-        h = clamped_glu(gu.to(x.dtype), limit, x.dtype, w[tok, slot])
+        xe = (x[tok].float() * w[tok, slot].float()[:, None]).to(x.dtype)
+        h = clamped_glu(xe.float() @ Wg.weight[e].float().t(), xe.float() @ Wu.weight[e].float().t(), limit, x.dtype)
         y.index_add_(0, tok, h.float() @ Wd.weight[e].float().t())
     return y
 

@@ -96,9 +96,16 @@ def clamped_expert(x, p, limit):
     return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ p["down"].T
 
 
+ROUTER_GAPS = []       # per router call: smallest distance, over its tokens, between the last chosen logit and the first one left out
+
+
 def router(h, w, top):
     """Scores ``sigmoid(W h)``; the ``top`` largest, weights = their scores as they are."""
-    s = torch.sigmoid(h @ w.T)
+    z = h @ w.T
+    if top < z.shape[-1]:
+        zs = torch.sort(z, dim=-1, descending=True).values
+        ROUTER_GAPS.append(float((zs[:, top - 1] - zs[:, top]).min()))
+    s = torch.sigmoid(z)
     wts, idx = torch.topk(s, top, dim=-1)
     return idx, wts
 
@@ -146,6 +153,13 @@ def forward(cfg, sd, tokens, dtype=torch.float64, layers_out=None):
         if layers_out is not None:
             layers_out.append(x.clone())
     return zero_centred_norm(x, sd["final.norm"], eps) @ sd["head"].T
+
+
+def min_router_gap(cfg, sd, tokens):
+    """How far the sequence's routing is from a close call (logit units; inf without routing decisions)."""
+    del ROUTER_GAPS[:]
+    forward(cfg, sd, tokens)
+    return min(ROUTER_GAPS, default=float("inf"))
 
 
 def tensor_shapes(cfg):
