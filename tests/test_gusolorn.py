@@ -259,7 +259,7 @@ def test_gates_that_saturate(device, dtype, tol):
 def test_grouped_expert_gemm_sizes(dtype, tol):
     """Width and expert rows that are multiples of 128: bf16 takes the grouped tensor-core GEMM for the routed experts (a 40-token
     prompt: sorted rows; single tokens: one weight-row read per pair in exact mode)."""
-    moe = dict(kind="moe", router=dict(experts=6, top=2), expert=dict(ff=64, limit=1.0), shared=dict(ff=32, limit=2.0))
+    moe = dict(kind="moe", router=dict(experts=6, top=2), expert=dict(ff=128, limit=1.0), shared=dict(ff=32, limit=2.0))
     cfgd = make_cfg([dict(MLSTM, mlp=moe), dict(ATTN, mlp=moe)], width=128)
     model, sd = make_model(cfgd, "cuda", dtype)
     t = pick(cfgd, sd, dtype, lambda s: toks(44, seed=s), 2, gap=0.05, tries=300)
